@@ -1,0 +1,184 @@
+/*
+ * libmoe_b200 -- C ABI of the B200 (sm_100a) MoE-block hot path.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream (as void*), launches on
+ * that stream without synchronising the host, and returns 0 on success or one of the MOE_B200_*
+ * status codes; moe_b200_last_error() gives the message of the calling thread's last failure.
+ * Nothing here allocates device memory unless its description says so: callers pass outputs and
+ * workspaces (sizes from the *_workspace_bytes functions).
+ *
+ * Each declaration names the reference interface it stands in for (paths inside the
+ * scale-snu/layered-prefill tree).
+ */
+#ifndef MOE_B200_H_
+#define MOE_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MOE_B200_OK 0
+#define MOE_B200_INVALID_ARGUMENT 1
+#define MOE_B200_CUDA_ERROR 2
+#define MOE_B200_WORKSPACE_TOO_SMALL 3
+#define MOE_B200_DEVICE_TIMEOUT 4
+#define MOE_B200_NOT_REGISTERED 5
+#define MOE_B200_DRIVER_ENTRY_POINT 6
+#define MOE_B200_TOO_LARGE 7
+
+#define MOE_B200_ACT_SILU 0      /* silu(gate) * up, w13 rows = [gate | up] */
+#define MOE_B200_ACT_SWIGLUOAI 1 /* gpt-oss gate, w13 rows interleaved gate/up, alpha 1.702, limit 7 */
+
+/* Message of the last non-zero status returned to this thread ("" if none). */
+const char* moe_b200_last_error(void);
+/* Library ABI version (bumped when a signature changes). */
+int moe_b200_abi_version(void);
+/* Token rows per grouped-GEMM tile = block size of the internal permutation (128). */
+int moe_b200_block_m(void);
+
+/*
+ * Router. Replaces ops.topk_softmax (csrc/ops.cpp:46-51, csrc/moe_topk_softmax_kernels.cu:476-503)
+ * and, with renormalize != 0, the division in fused_topk (nanovllm/layers/for_moe/fused_moe.py:417-418).
+ * gating: [T, E] row-major, fp32 (gating_is_bf16 == 0) or bf16 (!= 0). Outputs [T, k]:
+ * topk_weights fp32, topk_ids int32 (descending probability, ties to the lower expert id),
+ * token_expert_indices int32 = j*T + t (may be NULL).
+ */
+int moe_b200_topk_softmax(const void* gating, int gating_is_bf16, float* topk_weights, int32_t* topk_ids,
+                          int32_t* token_expert_indices, int T, int E, int k, int renormalize, void* stream);
+
+/*
+ * Permutation. Replaces ops.moe_align_block_size (csrc/ops.cpp:53-60,
+ * csrc/moe_align_block_size_kernels.cu:239-291). sorted_token_ids has sorted_cap =
+ * numel + E*(block_size-1) entries and is completely written (pads = numel); expert_ids has
+ * expert_ids_cap = ceil(sorted_cap / block_size) entries. Within an expert, ids are ascending.
+ * workspace: moe_b200_align_workspace_bytes(numel, E) bytes of device memory (the reference
+ * allocates its cumsum buffer itself, csrc/moe_align_block_size_kernels.cu:258-259).
+ */
+size_t moe_b200_align_workspace_bytes(int numel, int E);
+int moe_b200_moe_align_block_size(const int32_t* topk_ids, int numel, int E, int block_size,
+                                  int32_t* sorted_token_ids, int sorted_cap, int32_t* expert_ids, int expert_ids_cap,
+                                  int32_t* num_tokens_post_pad, void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * Stand-alone gated activations on bf16. Replace ops.silu_and_mul / ops.swigluoai_and_mul
+ * (csrc/ops.cpp:29-36, csrc/activation_kernels.cu:68-109). in: [rows, 2d], out: [rows, d].
+ */
+int moe_b200_silu_and_mul(void* out, const void* in, int rows, int d, void* stream);
+int moe_b200_swigluoai_and_mul(void* out, const void* in, int rows, int d, float alpha, float limit, void* stream);
+
+/*
+ * Sum over the k slots. Replaces moe_sum (nanovllm/layers/for_moe/moe_easy_kernel.py:26-31).
+ * in: bf16 [T, k, H]; out: bf16 [T, H]; fp32 accumulation in slot order.
+ */
+int moe_b200_moe_sum(const void* in, void* out, int T, int k, int H, void* stream);
+
+/*
+ * Both expert GEMMs, the activation, the routed-weight scaling and the k-slot sum.
+ * Replaces fused_experts / fused_experts_impl (nanovllm/layers/for_moe/fused_moe.py:422-633).
+ *   x    bf16 [T, H]           hidden states
+ *   w13  bf16 [E, 2*I, H]      gate rows then up rows (interleaved for MOE_B200_ACT_SWIGLUOAI)
+ *   w2   bf16 [E, H, I]        I = intermediate size held by this rank
+ *   w13_bias bf16 [E, 2*I], w2_bias bf16 [E, H]  (NULL when absent)
+ *   topk_weights fp32 [T, k], topk_ids int32 [T, k]
+ *   out  bf16 [T, H]; may be x itself (the reference's inplace=True)
+ *   status_word: one int32 of device memory that was zero when first handed to the library; a
+ *   kernel whose bounded wait ran out stores a non-zero code there (see moe_b200_read_status).
+ * Requires H % 16 == 0 and I % 16 == 0.
+ */
+size_t moe_b200_fused_experts_workspace_bytes(int T, int E, int top_k, int H, int I);
+int moe_b200_fused_experts(const void* x, const void* w13, const void* w2, const void* w13_bias, const void* w2_bias,
+                           const float* topk_weights, const int32_t* topk_ids, void* out, int T, int E, int top_k,
+                           int H, int I, int activation, void* workspace, size_t workspace_bytes,
+                           int32_t* status_word, void* stream);
+
+/*
+ * Router + fused_experts in one call: what FusedMoE.forward runs on one rank before the
+ * tensor-parallel reduction (nanovllm/layers/fused_moe.py:163-216, 750-787).
+ * router_logits: [T, E] bf16 (logits_is_bf16 != 0) or fp32. topk_weights_out / topk_ids_out may be
+ * NULL (the routing result then lives in the workspace only).
+ */
+size_t moe_b200_fused_moe_workspace_bytes(int T, int E, int top_k, int H, int I);
+int moe_b200_fused_moe_forward(const void* x, const void* router_logits, int logits_is_bf16, const void* w13,
+                               const void* w2, const void* w13_bias, const void* w2_bias, void* out,
+                               float* topk_weights_out, int32_t* topk_ids_out, int T, int E, int top_k, int H, int I,
+                               int renormalize, int activation, void* workspace, size_t workspace_bytes,
+                               int32_t* status_word, void* stream);
+
+/*
+ * Copies the device status word to the host after synchronising `stream`. Returns MOE_B200_OK and
+ * stores the word in *value; a non-zero word means a device-side wait timed out
+ * (1 operand stage never filled, 2 never drained, 3 accumulator never completed, 4 never released,
+ * 6 peer flag never arrived).
+ */
+int moe_b200_read_status(const int32_t* status_word, int32_t* value, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Tensor-parallel all-reduce over NVLink peer memory.
+ * Replaces the custom all-reduce ops (csrc/ops.cpp:77-95, csrc/custom_all_reduce_kernels.cu:15-191,
+ * csrc/custom_all_reduce.cuh:372-624). Handles are opaque int64 values, as in the reference (fptr_t).
+ * ---------------------------------------------------------------------------------------------- */
+
+/* Bytes of the synchronisation header at the start of every rank's metadata buffer
+ * (ops.meta_size, custom_all_reduce_kernels.cu:109). */
+int64_t moe_b200_ar_meta_size(void);
+/* cudaMalloc + cudaIpcGetMemHandle; writes 64 handle bytes (ops.allocate_shared_buffer_and_handle,
+ * custom_all_reduce_kernels.cu:148-179). This one allocates device memory by design. */
+int moe_b200_ar_allocate_shared_buffer(int64_t size_bytes, int64_t* ptr_out, uint8_t* handle_out /*[64]*/);
+/* cudaIpcOpenMemHandle (ops.open_mem_handle, custom_all_reduce_kernels.cu:181-187). */
+int moe_b200_ar_open_mem_handle(const uint8_t* handle /*[64]*/, int64_t* ptr_out);
+int moe_b200_ar_close_mem_handle(int64_t ptr);
+/* cudaFree (ops.free_shared_buffer, custom_all_reduce_kernels.cu:189-191). */
+int moe_b200_ar_free_shared_buffer(int64_t ptr);
+/* meta_ptrs[world_size]: every rank's metadata buffer as seen from this process (own pointer at
+ * [rank]); each must hold meta_size() + max_size bytes and start zeroed. rank_data: device scratch
+ * for registered pointer tuples (ops.init_custom_ar, custom_all_reduce_kernels.cu:15-33). */
+int moe_b200_ar_init(const int64_t* meta_ptrs, int world_size, void* rank_data, int64_t rank_data_bytes, int rank,
+                     int fully_connected, int64_t* handle_out);
+int moe_b200_ar_dispose(int64_t handle);
+/* ptrs[world_size]: one IPC-shared buffer per rank (ops.register_buffer, :115-123). */
+int moe_b200_ar_register_buffer(int64_t handle, const int64_t* ptrs);
+/* out = sum over ranks of inp (bf16/fp16/fp32 by element_size+is_bf16), fp32 accumulation in rank
+ * order, identical bits on every rank. If reg_buffer != 0 the input is first copied there
+ * (ops.all_reduce, custom_all_reduce_kernels.cu:64-107). algo: 0 auto, 1 one-shot, 2 two-shot. */
+int moe_b200_ar_all_reduce(int64_t handle, const void* inp, void* out, int64_t numel, int dtype /*0 bf16,1 f16,2 f32*/,
+                           int64_t reg_buffer, int64_t reg_buffer_bytes, int algo, int32_t* status_word, void* stream);
+/* k-slot sum of this rank's down-projection output fused with the all-reduce: one launch computes
+ * partial[t,:] = bf16(sum_j c3[t,j,:]) into this rank's registered buffer, meets the peers at a flag
+ * barrier and reduces across ranks into out. No reference counterpart as a single op: it stands for
+ * moe_sum (moe_easy_kernel.py:26-31) followed by tensor_model_parallel_all_reduce
+ * (nanovllm/layers/custom_all_reduce.py:343-366). */
+int moe_b200_ar_moe_sum_all_reduce(int64_t handle, const void* c3, void* out, int T, int k, int H, int64_t reg_buffer,
+                                   int64_t reg_buffer_bytes, int algo, int32_t* status_word, void* stream);
+/* Wall-clock limit of every device-side wait on a peer flag (default 2 s). After a wait ran out the
+ * status word is non-zero and the communicator's counters are out of step: dispose of it.
+ * (The reference spins without limit, csrc/custom_all_reduce.cuh:209,231-234.) */
+int moe_b200_ar_set_wait_limit_ns(int64_t handle, uint64_t limit_ns);
+/* Launches one thread that waits, with the given limit, on a flag of this rank's metadata buffer that
+ * nobody advances: a one-GPU check that a lost peer ends in a status word, not in a hang. No reference
+ * counterpart. */
+int moe_b200_ar_wait_probe(int64_t meta_ptr, uint64_t limit_ns, int32_t* status_word, void* stream);
+/* CUDA-graph support (ops.get_graph_buffer_ipc_meta / register_graph_buffers, :125-146):
+ * number of buffers captured since the last registration, their IPC handles (64 bytes each) and offsets. */
+int moe_b200_ar_graph_buffer_count(int64_t handle, int* count_out);
+int moe_b200_ar_get_graph_buffer_ipc_meta(int64_t handle, uint8_t* handles_out, int64_t* offsets_out, int capacity);
+int moe_b200_ar_register_graph_buffers(int64_t handle, const uint8_t* handles /*[world][count][64]*/,
+                                       const int64_t* offsets /*[world][count]*/, int count);
+
+/*
+ * Whole block on one tensor-parallel rank: router + experts + (moe_sum fused with all-reduce).
+ * ar_handle == 0 or world size 1: same as moe_b200_fused_moe_forward.
+ */
+int moe_b200_fused_moe_forward_tp(const void* x, const void* router_logits, int logits_is_bf16, const void* w13,
+                                  const void* w2, const void* w13_bias, const void* w2_bias, void* out, int T, int E,
+                                  int top_k, int H, int I, int renormalize, int activation, void* workspace,
+                                  size_t workspace_bytes, int64_t ar_handle, int64_t reg_buffer,
+                                  int64_t reg_buffer_bytes, int ar_algo, int32_t* status_word, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* MOE_B200_H_ */

@@ -1,0 +1,502 @@
+// Grouped expert GEMMs of the MoE block on the 5th-generation tensor cores.
+//
+// What the reference does with one Triton kernel called twice plus two element-wise kernels
+// (nanovllm/layers/for_moe/fused_moe.py:84-223, 575-631; csrc/activation_kernels.cu:9-25):
+//   pass 1 (gate_up): C1[r, :] = bf16(x[r / k] . w13[e]^T), h = bf16(bf16(silu(gate)) * up)
+//   pass 2 (down):    C3[r, :] = bf16((h[r] . w2[e]^T) * topk_w[r])
+// Here each pass is one persistent, warp-specialised kernel:
+//   * tiles are 128 permuted token rows (one block of the moe_align_block_size permutation with
+//     block size 128, so a tile never mixes experts) by up to 256 weight rows;
+//   * weights stream through TMA (3-D map [K, rows, expert], 128-byte swizzle, no cluster fan-out)
+//     into a 4-stage shared-memory ring; pass 1 gathers its token rows with 16-byte cp.async into the
+//     same swizzled layout, pass 2 reads the permuted intermediate with a 2-D TMA map;
+//   * one thread issues tcgen05.mma (M=128, N<=256, K=16 per instruction) into one of two 256-column
+//     TMEM accumulators, so the epilogue of tile i overlaps the main loop of tile i+1;
+//   * pass 1 keeps the gate rows and the matching up rows of w13 in the same tile (columns [0,BNH)
+//     and [BNH,2BNH) of the accumulator), so the activation is applied in registers with the
+//     reference's three bf16 roundings and only h is written, in permuted order;
+//   * pass 2 scales by the routed weight and writes bf16 rows at their flat index t*k+j.
+// The tile list is static: tile = blockIdx.x + i*gridDim.x over (m_block, n_tile), n fastest.
+#include <cstdio>
+
+#include "act_math.cuh"
+#include "moe_b200_internal.cuh"
+#include "ptx.cuh"
+
+namespace moe_b200 {
+
+namespace {
+
+constexpr int BM = kBlockM;
+constexpr int BK = 64;  // bf16 elements per K block = one 128-byte swizzle row
+constexpr int kUmmaK = 16;
+constexpr int kStages = 4;
+constexpr int kMaxBN = 256;
+constexpr int kABytes = BM * BK * 2;
+constexpr int kBBytes = kMaxBN * BK * 2;
+constexpr int kStageBytes = kABytes + kBBytes;
+constexpr int kAccCols = 256;
+constexpr int kTmemCols = 512;
+constexpr int kGatherLookahead = 2;
+constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+
+constexpr int kWarpTma = 0;
+constexpr int kWarpMma = 1;
+constexpr int kWarpEpilogue0 = 2;  // 4 warps
+constexpr int kWarpGather0 = 6;    // 4 warps (gate_up pass only)
+constexpr int kThreadsGateUp = 320;
+constexpr int kThreadsDown = 192;
+
+struct KernelParams {
+  const int* sorted_ids;
+  const int* expert_ids;
+  const int* num_post_pad;
+  const __nv_bfloat16* x;  // gate_up: token rows [T, K]
+  int numel;
+  int top_k;
+  int K;
+  int n_tiles;      // tiles along the output columns per m block
+  int tile_cols;    // output columns per tile
+  int mma_n;        // accumulator columns per tile (2*tile_cols for gate_up)
+  int out_cols;     // valid output columns (inter for gate_up, hidden for down)
+  int inter;        // row offset of the up half inside w13[e]
+  int interleaved;  // gate/up rows interleaved (swigluoai layout)
+  __nv_bfloat16* out;
+  long long out_ld;
+  const float* topk_w;
+  const __nv_bfloat16* bias;  // [E, 2*inter] (gate_up) or [E, hidden] (down), may be null
+  float alpha, limit;
+  int* status;
+};
+
+union Pack8 {
+  uint4 u;
+  __nv_bfloat16 h[8];
+};
+
+__device__ __forceinline__ void report(int* status, int code) { atomicCAS(status, 0, code); }
+
+template <int kMode>  // 1 = gate_up, 2 = down
+__global__ void __launch_bounds__(kMode == 1 ? kThreadsGateUp : kThreadsDown, 1)
+grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                    const KernelParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  // operand stages want 1024-byte alignment in the shared window (swizzle atoms, descriptor base offset 0)
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  uint64_t* bar_full = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
+  uint64_t* bar_empty = bar_full + kStages;
+  uint64_t* bar_tmem_full = bar_empty + kStages;
+  uint64_t* bar_tmem_empty = bar_tmem_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_tmem_empty + 2);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&bar_full[s], kMode == 1 ? 1 + 128 : 1);
+      mbar_init(&bar_empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&bar_tmem_full[a], 1);
+      mbar_init(&bar_tmem_empty[a], 4);
+    }
+    fence_mbar_init();
+    tma_prefetch_desc(&tmap_b);
+    if (kMode == 2) tma_prefetch_desc(&tmap_a);
+  }
+  if (warp == kWarpMma) {
+    tmem_alloc(tmem_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int num_m_blocks = *p.num_post_pad / BM;
+  const int total_tiles = num_m_blocks * p.n_tiles;
+  const int num_kb = (p.K + BK - 1) / BK;
+
+  if (warp == kWarpTma) {
+    // ------------------------------------------------------------------ TMA producer
+    uint32_t it = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      const int m_blk = tile / p.n_tiles;
+      const int n0 = (tile % p.n_tiles) * p.tile_cols;
+      const int e = p.expert_ids[m_blk];
+      for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        if (lane == 0) {
+          const uint32_t s = it % kStages;
+          const uint32_t ph = (it / kStages) & 1u;
+          ok = mbar_wait(&bar_empty[s], ph ^ 1u);
+          if (ok) {
+            uint8_t* a_dst = smem + s * kStageBytes;
+            uint8_t* b_dst = a_dst + kABytes;
+            if (kMode == 1) {
+              mbar_arrive_expect_tx(&bar_full[s], static_cast<uint32_t>(p.mma_n) * 128u);
+              if (p.interleaved) {
+                tma_load_3d(b_dst, &tmap_b, kb * BK, 2 * n0, e, &bar_full[s]);
+              } else {
+                tma_load_3d(b_dst, &tmap_b, kb * BK, n0, e, &bar_full[s]);
+                tma_load_3d(b_dst + p.tile_cols * 128, &tmap_b, kb * BK, p.inter + n0, e, &bar_full[s]);
+              }
+            } else {
+              mbar_arrive_expect_tx(&bar_full[s], static_cast<uint32_t>(kABytes) + static_cast<uint32_t>(p.mma_n) * 128u);
+              tma_load_2d(a_dst, &tmap_a, kb * BK, m_blk * BM, &bar_full[s]);
+              tma_load_3d(b_dst, &tmap_b, kb * BK, n0, e, &bar_full[s]);
+            }
+          } else {
+            report(p.status, kErrWaitEmpty);
+          }
+        }
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) break;
+      }
+    }
+  } else if (warp == kWarpMma) {
+    // ------------------------------------------------------------------ MMA issuer
+    const uint32_t idesc = umma_idesc_bf16(BM, static_cast<uint32_t>(p.mma_n));
+    uint32_t it = 0;
+    uint32_t tile_iter = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tile_iter) {
+      const uint32_t acc = tile_iter & 1u;
+      const uint32_t acc_ph = (tile_iter >> 1) & 1u;
+      if (lane == 0) {
+        ok = mbar_wait(&bar_tmem_empty[acc], acc_ph ^ 1u);
+        if (!ok) report(p.status, kErrWaitTmemEmpty);
+      }
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) break;
+      tc_fence_after_sync();
+      const uint32_t d_tmem = tmem_base + acc * kAccCols;
+      for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        if (lane == 0) {
+          const uint32_t s = it % kStages;
+          const uint32_t ph = (it / kStages) & 1u;
+          ok = mbar_wait(&bar_full[s], ph);
+          if (ok) {
+            tc_fence_after_sync();
+            const uint32_t a_addr = smem_u32(smem + s * kStageBytes);
+            const uint64_t adesc = umma_desc_k_sw128(a_addr);
+            const uint64_t bdesc = umma_desc_k_sw128(a_addr + kABytes);
+#pragma unroll
+            for (int k = 0; k < BK / kUmmaK; ++k) {
+              // advancing 16 bf16 = 32 bytes along K inside the swizzled row: +2 in 16-byte units
+              umma_bf16(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+            }
+            umma_commit(&bar_empty[s]);
+          } else {
+            report(p.status, kErrWaitFull);
+          }
+        }
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) break;
+      }
+      if (ok && lane == 0) umma_commit(&bar_tmem_full[acc]);
+      __syncwarp();
+    }
+  } else if (warp >= kWarpEpilogue0 && warp < kWarpEpilogue0 + 4) {
+    // ------------------------------------------------------------------ epilogue
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    const int row_in_tile = q * 32 + lane;
+    uint32_t tile_iter = 0;
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++tile_iter) {
+      const uint32_t acc = tile_iter & 1u;
+      const uint32_t acc_ph = (tile_iter >> 1) & 1u;
+      const int m_blk = tile / p.n_tiles;
+      const int n0 = (tile % p.n_tiles) * p.tile_cols;
+      const int e = p.expert_ids[m_blk];
+      const long long pos = static_cast<long long>(m_blk) * BM + row_in_tile;
+      const int flat = p.sorted_ids[pos];
+      const bool valid = flat < p.numel;
+      float w = 0.f;
+      if (kMode == 2 && valid) w = p.topk_w[flat];
+
+      bool ok = mbar_wait(&bar_tmem_full[acc], acc_ph);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) {
+        if (lane == 0) report(p.status, kErrWaitTmemFull);
+        break;
+      }
+      tc_fence_after_sync();
+
+      if (__any_sync(0xffffffffu, valid)) {
+        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * kAccCols;
+        if (kMode == 1) {
+          __nv_bfloat16* out_row = p.out + pos * p.out_ld;
+          if (!p.interleaved) {
+            const __nv_bfloat16* bias_g = p.bias ? p.bias + static_cast<long long>(e) * 2 * p.inter : nullptr;
+            for (int c = 0; c < p.tile_cols; c += 16) {
+              uint32_t g[16], u[16];
+              tmem_ld_x16(taddr + c, g);
+              tmem_ld_x16(taddr + p.tile_cols + c, u);
+              tmem_ld_wait();
+              const int col = n0 + c;
+              if (valid && col < p.out_cols) {
+                Pack8 o[2];
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                  float gf = __uint_as_float(g[j]);
+                  float uf = __uint_as_float(u[j]);
+                  if (bias_g) {
+                    gf += __bfloat162float(bias_g[col + j]);
+                    uf += __bfloat162float(bias_g[p.inter + col + j]);
+                  }
+                  o[j >> 3].h[j & 7] = silu_mul_bf16(__float2bfloat16_rn(gf), __float2bfloat16_rn(uf));
+                }
+                *reinterpret_cast<uint4*>(out_row + col) = o[0].u;
+                *reinterpret_cast<uint4*>(out_row + col + 8) = o[1].u;
+              }
+            }
+          } else {
+            const __nv_bfloat16* bias_g = p.bias ? p.bias + static_cast<long long>(e) * 2 * p.inter : nullptr;
+            for (int c = 0; c < p.tile_cols; c += 8) {
+              uint32_t gu[16];
+              tmem_ld_x16(taddr + 2 * c, gu);
+              tmem_ld_wait();
+              const int col = n0 + c;
+              if (valid && col < p.out_cols) {
+                Pack8 o;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                  float gf = __uint_as_float(gu[2 * j]);
+                  float uf = __uint_as_float(gu[2 * j + 1]);
+                  if (bias_g) {
+                    gf += __bfloat162float(bias_g[2 * (col + j)]);
+                    uf += __bfloat162float(bias_g[2 * (col + j) + 1]);
+                  }
+                  o.h[j] = swigluoai_bf16(__float2bfloat16_rn(gf), __float2bfloat16_rn(uf), p.alpha, p.limit);
+                }
+                *reinterpret_cast<uint4*>(out_row + col) = o.u;
+              }
+            }
+          }
+        } else {
+          __nv_bfloat16* out_row = p.out + static_cast<long long>(valid ? flat : 0) * p.out_ld;
+          const __nv_bfloat16* bias_d = p.bias ? p.bias + static_cast<long long>(e) * p.out_cols : nullptr;
+          for (int c = 0; c < p.tile_cols; c += 16) {
+            uint32_t d[16];
+            tmem_ld_x16(taddr + c, d);
+            tmem_ld_wait();
+            const int col = n0 + c;
+            if (valid && col < p.out_cols) {
+              Pack8 o[2];
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                float v = __uint_as_float(d[j]);
+                if (bias_d) v += __bfloat162float(bias_d[col + j]);
+                o[j >> 3].h[j & 7] = __float2bfloat16_rn(v * w);
+              }
+              *reinterpret_cast<uint4*>(out_row + col) = o[0].u;
+              *reinterpret_cast<uint4*>(out_row + col + 8) = o[1].u;
+            }
+          }
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar_tmem_empty[acc]);
+    }
+  } else if (kMode == 1 && warp >= kWarpGather0) {
+    // ------------------------------------------------------------------ token-row gather (gate_up pass)
+    const int gw = warp - kWarpGather0;  // 0..3
+    const int sub = lane >> 3;           // row inside a group of 4
+    const int ch = lane & 7;             // 16-byte chunk inside the 128-byte row
+    const int row0 = gw * 4 + sub;       // rows handled: row0 + 16*i
+    const uint32_t swz = static_cast<uint32_t>((ch ^ (row0 & 7)) << 4);
+    uint32_t it = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      const int m_blk = tile / p.n_tiles;
+      const __nv_bfloat16* src[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int flat = p.sorted_ids[static_cast<long long>(m_blk) * BM + row0 + 16 * i];
+        src[i] = flat < p.numel ? p.x + static_cast<long long>(flat / p.top_k) * p.K + ch * 8 : nullptr;
+      }
+      for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        const uint32_t s = it % kStages;
+        const uint32_t ph = (it / kStages) & 1u;
+        ok = mbar_wait(&bar_empty[s], ph ^ 1u);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) {
+          if (lane == 0) report(p.status, kErrWaitEmpty);
+          break;
+        }
+        const uint32_t a_base = smem_u32(smem + s * kStageBytes);
+        const bool in_k = kb * BK + ch * 8 < p.K;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const uint32_t dst = a_base + static_cast<uint32_t>(row0 + 16 * i) * 128u + swz;
+          const bool live = in_k && src[i] != nullptr;
+          cp_async_16(dst, live ? static_cast<const void*>(src[i] + kb * BK) : static_cast<const void*>(p.x),
+                      live ? 16u : 0u);
+        }
+        cp_async_commit();
+        if (it >= kGatherLookahead) {
+          cp_async_wait<kGatherLookahead>();
+          fence_proxy_async_smem();
+          mbar_arrive(&bar_full[(it - kGatherLookahead) % kStages]);
+        }
+      }
+    }
+    cp_async_wait<0>();
+    fence_proxy_async_smem();
+    if (ok) {
+      for (uint32_t j = it >= kGatherLookahead ? it - kGatherLookahead : 0; j < it; ++j)
+        mbar_arrive(&bar_full[j % kStages]);
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  if (warp == kWarpMma) tmem_dealloc(tmem_base, kTmemCols);
+}
+
+// ---------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+  }
+  return fn;
+}
+
+// bf16 tensor, innermost dimension contiguous; dims/box given innermost first.
+int make_map(CUtensorMap* map, const void* base, int rank, const uint64_t* dims, const uint32_t* box) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (fn == nullptr) return set_error(kStatusDriverEntryPoint, "cuTensorMapEncodeTiled is not available from this driver");
+  cuuint64_t gdim[3];
+  cuuint64_t gstride[2];
+  cuuint32_t bdim[3];
+  cuuint32_t estr[3] = {1, 1, 1};
+  uint64_t stride = 2;
+  for (int i = 0; i < rank; ++i) {
+    gdim[i] = dims[i];
+    bdim[i] = box[i];
+    stride *= dims[i];
+    if (i + 1 < rank) gstride[i] = stride;
+  }
+  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, static_cast<cuuint32_t>(rank), const_cast<void*>(base),
+                        gdim, gstride, bdim, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return set_error(kStatusCudaError, "cuTensorMapEncodeTiled failed with CUresult %d", static_cast<int>(r));
+  return kStatusOk;
+}
+
+template <int kMode>
+int ensure_smem_attr() {
+  static bool done = false;
+  if (!done) {
+    const cudaError_t e = cudaFuncSetAttribute(grouped_gemm_kernel<kMode>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    if (e != cudaSuccess) return check_cuda(e, "cudaFuncSetAttribute(grouped_gemm_kernel)");
+    done = true;
+  }
+  return kStatusOk;
+}
+
+int pick_gate_up_tile(int inter) {
+  for (int c = 128; c >= 16; c -= 16)
+    if (inter % c == 0) return c;
+  return 0;
+}
+
+int check_common(const GroupedGemmArgs& a) {
+  if (a.hidden <= 0 || a.inter <= 0 || a.hidden % 8 != 0 || a.inter % 16 != 0)
+    return set_error(kStatusInvalidArgument, "grouped GEMM: hidden must be a multiple of 8 and the per-rank intermediate size a multiple of 16 (got %d, %d)", a.hidden, a.inter);
+  if (a.top_k <= 0 || a.numel < 0 || a.max_m_blocks < 0 || a.status == nullptr)
+    return set_error(kStatusInvalidArgument, "grouped GEMM: bad routing sizes or null status word");
+  return kStatusOk;
+}
+
+}  // namespace
+
+int device_sm_count() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
+int launch_grouped_gemm1(const GroupedGemmArgs& a, const __nv_bfloat16* x, const __nv_bfloat16* w13,
+                         const __nv_bfloat16* w13_bias, __nv_bfloat16* h_sorted, int rows_cap, cudaStream_t stream) {
+  if (int st = check_common(a)) return st;
+  if (a.numel == 0 || a.max_m_blocks == 0) return kStatusOk;
+  const int tile_cols = pick_gate_up_tile(a.inter);
+  const int mma_n = 2 * tile_cols;
+  if (int st = ensure_smem_attr<1>()) return st;
+
+  CUtensorMap map_b, map_a;
+  memset(&map_a, 0, sizeof(map_a));
+  const uint64_t dims[3] = {static_cast<uint64_t>(a.hidden), static_cast<uint64_t>(2 * a.inter), static_cast<uint64_t>(a.num_experts)};
+  const uint32_t box[3] = {BK, static_cast<uint32_t>(a.activation == 1 ? mma_n : tile_cols), 1};
+  if (int st = make_map(&map_b, w13, 3, dims, box)) return st;
+
+  KernelParams p{};
+  p.sorted_ids = a.sorted_ids; p.expert_ids = a.expert_ids; p.num_post_pad = a.num_post_pad;
+  p.x = x; p.numel = a.numel; p.top_k = a.top_k; p.K = a.hidden;
+  p.n_tiles = a.inter / tile_cols; p.tile_cols = tile_cols; p.mma_n = mma_n; p.out_cols = a.inter; p.inter = a.inter;
+  p.interleaved = a.activation == 1 ? 1 : 0;
+  p.out = h_sorted; p.out_ld = a.inter; p.topk_w = nullptr; p.bias = w13_bias;
+  p.alpha = a.act_alpha; p.limit = a.act_limit; p.status = a.status;
+  (void)rows_cap;
+
+  long long tiles = static_cast<long long>(a.max_m_blocks) * p.n_tiles;
+  const int grid = static_cast<int>(tiles < device_sm_count() ? tiles : device_sm_count());
+  grouped_gemm_kernel<1><<<grid, kThreadsGateUp, kSmemBytes, stream>>>(map_a, map_b, p);
+  return check_launch("grouped_gemm gate_up");
+}
+
+int launch_grouped_gemm2(const GroupedGemmArgs& a, const __nv_bfloat16* h_sorted, int rows_cap,
+                         const __nv_bfloat16* w2, const __nv_bfloat16* w2_bias, const float* topk_w,
+                         __nv_bfloat16* c3, cudaStream_t stream) {
+  if (int st = check_common(a)) return st;
+  if (a.numel == 0 || a.max_m_blocks == 0) return kStatusOk;
+  if (a.hidden % 16 != 0) return set_error(kStatusInvalidArgument, "grouped GEMM down: hidden must be a multiple of 16");
+  // 256-column tiles once there is more than one token block per expert on average, else 128.
+  int tile_cols = a.max_m_blocks > 2 * a.num_experts ? 256 : 128;
+  if (a.hidden < tile_cols) tile_cols = (a.hidden + 15) / 16 * 16;
+  if (int st = ensure_smem_attr<2>()) return st;
+
+  CUtensorMap map_a, map_b;
+  const uint64_t dims_a[2] = {static_cast<uint64_t>(a.inter), static_cast<uint64_t>(rows_cap)};
+  const uint32_t box_a[2] = {BK, BM};
+  if (int st = make_map(&map_a, h_sorted, 2, dims_a, box_a)) return st;
+  const uint64_t dims_b[3] = {static_cast<uint64_t>(a.inter), static_cast<uint64_t>(a.hidden), static_cast<uint64_t>(a.num_experts)};
+  const uint32_t box_b[3] = {BK, static_cast<uint32_t>(tile_cols), 1};
+  if (int st = make_map(&map_b, w2, 3, dims_b, box_b)) return st;
+
+  KernelParams p{};
+  p.sorted_ids = a.sorted_ids; p.expert_ids = a.expert_ids; p.num_post_pad = a.num_post_pad;
+  p.x = nullptr; p.numel = a.numel; p.top_k = a.top_k; p.K = a.inter;
+  p.n_tiles = (a.hidden + tile_cols - 1) / tile_cols; p.tile_cols = tile_cols; p.mma_n = tile_cols;
+  p.out_cols = a.hidden; p.inter = a.inter; p.interleaved = 0;
+  p.out = c3; p.out_ld = a.hidden; p.topk_w = topk_w; p.bias = w2_bias;
+  p.alpha = 0.f; p.limit = 0.f; p.status = a.status;
+
+  long long tiles = static_cast<long long>(a.max_m_blocks) * p.n_tiles;
+  const int grid = static_cast<int>(tiles < device_sm_count() ? tiles : device_sm_count());
+  grouped_gemm_kernel<2><<<grid, kThreadsDown, kSmemBytes, stream>>>(map_a, map_b, p);
+  return check_launch("grouped_gemm down");
+}
+
+}  // namespace moe_b200

@@ -1,0 +1,74 @@
+// Declarations shared by the translation units of libmoe_b200: status codes, the
+// error-string slot behind moe_b200_last_error(), and the internal launchers that
+// the extern "C" layer (c_api.cu) forwards to.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+namespace moe_b200 {
+
+enum : int {
+  kStatusOk = 0,
+  kStatusInvalidArgument = 1,
+  kStatusCudaError = 2,
+  kStatusWorkspaceTooSmall = 3,
+  kStatusDeviceTimeout = 4,   // a bounded device-side wait ran out (see the kernel's status word)
+  kStatusNotRegistered = 5,   // all-reduce: buffer address is not registered
+  kStatusDriverEntryPoint = 6,
+  kStatusTooLarge = 7,        // request exceeds a fixed capacity (static scratch)
+};
+
+int set_error(int status, const char* fmt, ...);
+int check_launch(const char* what);
+int check_cuda(cudaError_t e, const char* what);
+const char* last_error_string();
+
+constexpr int kBlockM = 128;  // token rows per grouped-GEMM tile (and the internal permutation block)
+
+// ---- routing.cu
+int launch_topk_softmax(const void* gating, int gating_is_bf16, float* topk_w, int* topk_ids,
+                        int* token_expert_indices, int T, int E, int k, int renormalize, cudaStream_t stream);
+
+// ---- align.cu
+size_t align_workspace_bytes(int numel, int E);
+int launch_align_block_size(const int* topk_ids, int numel, int E, int block_size, int* sorted_ids, int sorted_cap,
+                            int* expert_ids, int expert_ids_cap, int* num_post_pad, void* workspace,
+                            size_t workspace_bytes, cudaStream_t stream);
+
+// ---- elementwise.cu
+int launch_silu_and_mul(__nv_bfloat16* out, const __nv_bfloat16* in, int rows, int d, cudaStream_t stream);
+int launch_swigluoai_and_mul(__nv_bfloat16* out, const __nv_bfloat16* in, int rows, int d, float alpha, float limit,
+                             cudaStream_t stream);
+int launch_moe_sum(const __nv_bfloat16* in, __nv_bfloat16* out, int T, int k, int H, cudaStream_t stream);
+
+// ---- grouped_gemm.cu
+struct GroupedGemmArgs {
+  // permutation (block size kBlockM)
+  const int* sorted_ids;
+  const int* expert_ids;
+  const int* num_post_pad;
+  int numel;        // T * top_k
+  int top_k;
+  int max_m_blocks; // upper bound on number of kBlockM blocks (sizes the grid)
+  int num_experts;
+  // problem
+  int hidden;       // H
+  int inter;        // I per rank
+  int activation;   // 0 silu, 1 swigluoai (interleaved gate/up)
+  float act_alpha, act_limit;
+  int* status;      // device status word (0 = ok)
+};
+// h_sorted[p, :] = act(x[sorted_ids[p] / top_k] @ w13[e]^T), p in permuted order, bf16 [rows_cap, inter]
+int launch_grouped_gemm1(const GroupedGemmArgs& a, const __nv_bfloat16* x, const __nv_bfloat16* w13,
+                         const __nv_bfloat16* w13_bias, __nv_bfloat16* h_sorted, int rows_cap, cudaStream_t stream);
+// c3[f, :] = bf16((h_sorted[p] @ w2[e]^T) * topk_w[f]), f = sorted_ids[p], bf16 [numel, hidden]
+int launch_grouped_gemm2(const GroupedGemmArgs& a, const __nv_bfloat16* h_sorted, int rows_cap,
+                         const __nv_bfloat16* w2, const __nv_bfloat16* w2_bias, const float* topk_w,
+                         __nv_bfloat16* c3, cudaStream_t stream);
+int device_sm_count();
+
+}  // namespace moe_b200

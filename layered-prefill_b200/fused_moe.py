@@ -1,0 +1,176 @@
+"""Host-side mirror of nanovllm/layers/for_moe/fused_moe.py: `fused_topk`, `moe_align_block_size`,
+`fused_experts` / `fused_experts_impl` with the reference's signatures, backed by libmoe_b200.
+
+What is different underneath: one C call runs permutation, both grouped tcgen05 GEMMs (activation
+and routed-weight scaling in their epilogues) and the k-slot sum on the current stream; the tile
+shape is chosen inside the library from the shapes, so there is no Triton config lookup
+(for_moe/fused_moe.py:318-390 has no counterpart here). Quantised paths are rejected, as they are
+by the reference's asserts (for_moe/fused_moe.py:248-249,571,607).
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+
+from . import ops
+from ._lib import ACT_CODES, check, lib
+
+
+def cdiv(a: int, b: int) -> int:
+    return -(-a // b)
+
+
+def fused_topk(hidden_states: torch.Tensor, gating_output: torch.Tensor, topk: int, renormalize: bool):
+    """for_moe/fused_moe.py:393-419. Returns (topk_weights f32 [M,k], topk_ids i32 [M,k],
+    token_expert_indices i32 [M,k]). bf16 logits are consumed directly (the upcast is exact) and the
+    renormalisation is applied by the same kernel."""
+    assert hidden_states.shape[0] == gating_output.shape[0], "Number of tokens mismatch"
+    M = hidden_states.shape[0]
+    dev = hidden_states.device
+    topk_weights = torch.empty(M, topk, dtype=torch.float32, device=dev)
+    topk_ids = torch.empty(M, topk, dtype=torch.int32, device=dev)
+    token_expert_indices = torch.empty(M, topk, dtype=torch.int32, device=dev)
+    g = gating_output if gating_output.dtype in (torch.float32, torch.bfloat16) else gating_output.float()
+    g = g.contiguous()
+    E = g.size(-1)
+    with torch.cuda.device(dev):
+        check(lib.moe_b200_topk_softmax(g.data_ptr(), int(g.dtype == torch.bfloat16), topk_weights.data_ptr(),
+                                        topk_ids.data_ptr(), token_expert_indices.data_ptr(), M, E, topk,
+                                        int(bool(renormalize)), torch.cuda.current_stream().cuda_stream))
+    return topk_weights, topk_ids, token_expert_indices
+
+
+def moe_align_block_size(topk_ids: torch.Tensor, block_size: int, num_experts: int
+                         ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """for_moe/fused_moe.py:17-70: same buffer sizes and fill value; ids inside an expert come out in
+    ascending order (the reference leaves that order to atomic arrival)."""
+    max_num_tokens_padded = topk_ids.numel() + num_experts * (block_size - 1)
+    sorted_ids = torch.empty((max_num_tokens_padded,), dtype=torch.int32, device=topk_ids.device)
+    max_num_m_blocks = cdiv(max_num_tokens_padded, block_size)
+    expert_ids = torch.empty((max_num_m_blocks,), dtype=torch.int32, device=topk_ids.device)
+    num_tokens_post_pad = torch.empty((1), dtype=torch.int32, device=topk_ids.device)
+    ops.moe_align_block_size(topk_ids, num_experts, block_size, sorted_ids, expert_ids, num_tokens_post_pad)
+    return sorted_ids, expert_ids, num_tokens_post_pad
+
+
+class _Workspaces:
+    """One growing scratch tensor per device, reused across calls (stable address, no per-call malloc)."""
+
+    def __init__(self) -> None:
+        self._buf: dict[int, torch.Tensor] = {}
+
+    def get(self, device: torch.device, nbytes: int) -> torch.Tensor:
+        idx = device.index if device.index is not None else torch.cuda.current_device()
+        cur = self._buf.get(idx)
+        if cur is None or cur.numel() < nbytes:
+            cur = torch.empty(max(nbytes, 1), dtype=torch.uint8, device=torch.device("cuda", idx))
+            self._buf[idx] = cur
+        return cur
+
+
+_workspaces = _Workspaces()
+
+
+def _check_experts_args(hidden_states, w1, w2, topk_weights, topk_ids, activation, **quant):
+    assert hidden_states.size(1) == w1.size(2), f"Hidden size mismatch {hidden_states.size(1)} != {w1.size(2)}"
+    assert topk_weights.size() == topk_ids.size(), "topk shape mismatch"
+    assert hidden_states.is_contiguous(), "Hidden_states must be contiguous"
+    assert w1.stride(-1) == 1, "Stride of last dimension must be 1"
+    assert w2.stride(-1) == 1, "Stride of last dimension must be 1"
+    if hidden_states.dtype != torch.bfloat16 or w1.dtype != torch.bfloat16 or w2.dtype != torch.bfloat16:
+        raise ValueError(f"Unsupported compute_type: {hidden_states.dtype} (this build computes in bfloat16)")
+    if activation not in ACT_CODES:
+        raise ValueError(f"Unsupported FusedMoe activation: {activation}")
+    for name, v in quant.items():
+        assert v is None, f"{name} is not supported (the reference asserts the same)"
+    if not hidden_states.is_cuda:
+        raise RuntimeError("fused_experts needs CUDA tensors; there is no CPU path")
+    assert w1.is_contiguous() and w2.is_contiguous(), "expert weights must be contiguous [E, 2I, H] / [E, H, I]"
+
+
+def fused_experts_impl(hidden_states: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor, topk_weights: torch.Tensor,
+                       topk_ids: torch.Tensor, inplace: bool = False, activation: str = "silu",
+                       apply_router_weight_on_input: bool = False, per_channel_quant: bool = False,
+                       global_num_experts: int = -1, expert_map: Optional[torch.Tensor] = None,
+                       w1_scale=None, w2_scale=None, w1_zp=None, w2_zp=None, a1_scale=None, a2_scale=None,
+                       block_shape=None, w1_bias: Optional[torch.Tensor] = None,
+                       w2_bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """for_moe/fused_moe.py:461-633."""
+    _check_experts_args(hidden_states, w1, w2, topk_weights, topk_ids, activation, w1_scale=w1_scale,
+                        w2_scale=w2_scale, w1_zp=w1_zp, w2_zp=w2_zp, a1_scale=a1_scale, a2_scale=a2_scale,
+                        block_shape=block_shape, expert_map=expert_map)
+    if apply_router_weight_on_input:
+        raise NotImplementedError("apply_router_weight_on_input=True is not used by the reference's models")
+    T, H = hidden_states.shape
+    E, two_i, _ = w1.shape
+    inter = two_i // 2
+    assert w2.shape == (E, H, inter), f"w2 shape {tuple(w2.shape)} does not match w13 {tuple(w1.shape)}"
+    if global_num_experts not in (-1, E):
+        raise NotImplementedError("expert parallelism (global_num_experts != local) is not part of the reference's path")
+    k = topk_ids.size(1)
+    out = hidden_states if inplace else torch.empty_like(hidden_states)
+    if T == 0:
+        return out
+    tw = topk_weights.to(torch.float32).contiguous()
+    ti = topk_ids.to(torch.int32).contiguous()
+    dev = hidden_states.device
+    nbytes = lib.moe_b200_fused_experts_workspace_bytes(T, E, k, H, inter)
+    ws = _workspaces.get(dev, nbytes)
+    with torch.cuda.device(dev):
+        check(lib.moe_b200_fused_experts(
+            hidden_states.data_ptr(), w1.data_ptr(), w2.data_ptr(),
+            w1_bias.data_ptr() if w1_bias is not None else 0, w2_bias.data_ptr() if w2_bias is not None else 0,
+            tw.data_ptr(), ti.data_ptr(), out.data_ptr(), T, E, k, H, inter, ACT_CODES[activation],
+            ws.data_ptr(), ws.numel(), ops.status_word(dev).data_ptr(), torch.cuda.current_stream().cuda_stream))
+    return out
+
+
+def fused_experts(hidden_states: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor, w1_bias: Optional[torch.Tensor],
+                  w2_bias: Optional[torch.Tensor], topk_weights: torch.Tensor, topk_ids: torch.Tensor,
+                  inplace: bool = False, activation: str = "silu", apply_router_weight_on_input: bool = False,
+                  per_channel_quant: bool = False, global_num_experts: int = -1,
+                  expert_map: Optional[torch.Tensor] = None, w1_scale=None, w2_scale=None, w1_zp=None, w2_zp=None,
+                  a1_scale=None, a2_scale=None, block_shape=None, allow_deep_gemm: bool = False) -> torch.Tensor:
+    """for_moe/fused_moe.py:422-460."""
+    return fused_experts_impl(hidden_states, w1, w2, topk_weights, topk_ids, inplace, activation,
+                              apply_router_weight_on_input, per_channel_quant, global_num_experts, expert_map,
+                              w1_scale, w2_scale, w1_zp, w2_zp, a1_scale, a2_scale, block_shape, w1_bias, w2_bias)
+
+
+def fused_moe_forward(hidden_states: torch.Tensor, router_logits: torch.Tensor, w13: torch.Tensor, w2: torch.Tensor,
+                      top_k: int, renormalize: bool = True, activation: str = "silu", inplace: bool = True,
+                      w13_bias: Optional[torch.Tensor] = None, w2_bias: Optional[torch.Tensor] = None,
+                      comm=None) -> torch.Tensor:
+    """Router + experts (+ tensor-parallel reduction when `comm` is an initialised CustomAllreduce) through
+    one library call: what FusedMoE.forward followed by maybe_all_reduce_tensor_model_parallel does
+    (nanovllm/layers/fused_moe.py:746-787, nanovllm/models/qwen3_moe.py:99-116)."""
+    _check_experts_args(hidden_states, w13, w2, router_logits[:, :top_k], router_logits[:, :top_k], activation)
+    T, H = hidden_states.shape
+    E, two_i, _ = w13.shape
+    inter = two_i // 2
+    assert router_logits.shape == (T, E)
+    logits = router_logits if router_logits.dtype in (torch.bfloat16, torch.float32) else router_logits.float()
+    logits = logits.contiguous()
+    out = hidden_states if inplace else torch.empty_like(hidden_states)
+    if T == 0:
+        return out
+    dev = hidden_states.device
+    nbytes = lib.moe_b200_fused_moe_workspace_bytes(T, E, top_k, H, inter)
+    ws = _workspaces.get(dev, nbytes)
+    stream = torch.cuda.current_stream().cuda_stream
+    b13 = w13_bias.data_ptr() if w13_bias is not None else 0
+    b2 = w2_bias.data_ptr() if w2_bias is not None else 0
+    with torch.cuda.device(dev):
+        if comm is not None and not comm.disabled and comm.world_size > 1:
+            check(lib.moe_b200_fused_moe_forward_tp(
+                hidden_states.data_ptr(), logits.data_ptr(), int(logits.dtype == torch.bfloat16), w13.data_ptr(),
+                w2.data_ptr(), b13, b2, out.data_ptr(), T, E, top_k, H, inter, int(bool(renormalize)),
+                ACT_CODES[activation], ws.data_ptr(), ws.numel(), comm._ptr, comm.buffer_ptrs[comm.rank],
+                comm.max_size, 0, ops.status_word(dev).data_ptr(), stream))
+        else:
+            check(lib.moe_b200_fused_moe_forward(
+                hidden_states.data_ptr(), logits.data_ptr(), int(logits.dtype == torch.bfloat16), w13.data_ptr(),
+                w2.data_ptr(), b13, b2, out.data_ptr(), 0, 0, T, E, top_k, H, inter, int(bool(renormalize)),
+                ACT_CODES[activation], ws.data_ptr(), ws.numel(), ops.status_word(dev).data_ptr(), stream))
+    return out

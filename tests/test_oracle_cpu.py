@@ -1,0 +1,153 @@
+"""The CPU oracle against the reference-derived golden vectors and hand-checkable cases."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import moe_oracle as O
+
+
+@pytest.mark.parametrize("name", ["route_a", "route_b", "route_c", "route_d"])
+def test_routing_matches_reference_helper(golden, name):
+    logits = torch.from_numpy(golden[f"{name}_logits"])
+    k = golden[f"{name}_ids"].shape[1]
+    w, ids, tei = O.topk_softmax(logits, k, renormalize=True)
+    assert np.array_equal(ids.numpy(), golden[f"{name}_ids"])
+    np.testing.assert_allclose(w.numpy(), golden[f"{name}_weights"], rtol=2e-6, atol=1e-7)
+    T = logits.shape[0]
+    assert np.array_equal(tei.numpy(), (np.arange(k)[None, :] * T + np.arange(T)[:, None]).astype(np.int32))
+
+
+def test_routing_unnormalised_is_full_softmax(golden):
+    logits = torch.from_numpy(golden["route_a_logits"])
+    w, ids, _ = O.topk_softmax(logits, 8, renormalize=False)
+    p = torch.softmax(logits, dim=-1)
+    np.testing.assert_allclose(w.numpy(), torch.gather(p, 1, ids.long()).numpy(), rtol=3e-6, atol=1e-8)
+    assert (w[:, :-1] >= w[:, 1:]).all()  # slots in descending probability
+
+
+def test_routing_ties_go_to_lowest_index():
+    logits = torch.zeros(3, 4)
+    logits[1] = torch.tensor([1.0, 2.0, 2.0, 1.0])
+    logits[2] = torch.tensor([5.0, 5.0, 5.0, 5.0])
+    _, ids, _ = O.topk_softmax(logits, 2)
+    assert ids.tolist() == [[0, 1], [1, 2], [0, 1]]
+
+
+def test_routing_non_power_of_two():
+    g = torch.Generator().manual_seed(3)
+    logits = torch.randn(11, 96, generator=g)
+    w, ids, _ = O.topk_softmax(logits, 4, renormalize=False)
+    p = torch.softmax(logits, -1)
+    tv, ti = torch.topk(p, 4, dim=-1)
+    assert torch.equal(ids.long(), ti)
+    np.testing.assert_allclose(w.numpy(), tv.numpy(), rtol=3e-6)
+
+
+def test_activation_and_sum_match_reference_helpers(golden):
+    x = torch.from_numpy(golden["silu_in"])
+    ours = O.silu_and_mul(x.to(torch.bfloat16)).float().numpy()
+    np.testing.assert_allclose(ours, golden["silu_out"], rtol=2 ** -6, atol=1e-3)  # two bf16 roundings
+    x = torch.from_numpy(golden["swiglu_in"])
+    ours = O.swigluoai_and_mul(x.to(torch.bfloat16)).float().numpy()
+    np.testing.assert_allclose(ours, golden["swiglu_out"], rtol=2 ** -7, atol=1e-3)
+    c3 = torch.from_numpy(golden["sum_in"]).to(torch.bfloat16)
+    assert np.array_equal(O.moe_sum(c3).float().numpy(), golden["sum_out"])  # bit-exact
+
+
+def _align_by_hand(ids, bs, E):
+    ids = ids.reshape(-1).tolist()
+    numel = len(ids)
+    out, eids = [], []
+    for e in range(E):
+        mine = [i for i, v in enumerate(ids) if v == e]
+        if not mine:
+            continue
+        pad = (-len(mine)) % bs
+        out += mine + [numel] * pad
+        eids += [e] * ((len(mine) + pad) // bs)
+    return out, eids
+
+
+@pytest.mark.parametrize("T,k,E,bs", [(3, 2, 4, 4), (17, 2, 8, 16), (64, 8, 128, 16), (5, 1, 3, 1), (40, 4, 16, 128)])
+def test_align_against_hand_rolled(T, k, E, bs):
+    g = torch.Generator().manual_seed(T * 131 + E)
+    ids = torch.stack([torch.randperm(E, generator=g)[:k] for _ in range(T)]).to(torch.int32)
+    s, e, post = O.moe_align_block_size(ids, bs, E)
+    hs, he = _align_by_hand(ids, bs, E)
+    assert int(post) == len(hs)
+    assert s[:len(hs)].tolist() == hs
+    assert (s[len(hs):] == T * k).all()
+    assert e[:len(he)].tolist() == he
+    assert (e[len(he):] == 0).all()
+    assert s.numel() == T * k + E * (bs - 1)
+
+
+def test_align_edge_cases():
+    # an expert with exactly block_size tokens, one with none, ids out of range are skipped
+    ids = torch.tensor([[0, 2], [0, 2], [0, 3], [0, 7]], dtype=torch.int32)
+    s, e, post = O.moe_align_block_size(ids, 4, 4)
+    assert int(post) == 12
+    assert s[:12].tolist() == [0, 2, 4, 6, 1, 3, 8, 8, 5, 8, 8, 8]
+    assert e[:3].tolist() == [0, 2, 3]
+    s, e, post = O.moe_align_block_size(torch.zeros(0, 2, dtype=torch.int32), 4, 4)
+    assert int(post) == 0 and (s == 0).all()
+
+
+def test_canonicalize_is_order_free():
+    ids = torch.tensor([[1, 0], [1, 0], [0, 1]], dtype=torch.int32)
+    s, e, post = O.moe_align_block_size(ids, 4, 2)
+    shuffled = s.clone()
+    shuffled[0:3] = s[[2, 0, 1]]
+    c = O.canonicalize_sorted_ids(shuffled, e, int(post), 4, 6)
+    assert torch.equal(c, s)
+
+
+def test_expert_loop_matches_dense_formula():
+    g = torch.Generator().manual_seed(0)
+    T, H, E, k, I = 9, 32, 4, 2, 16
+    x = torch.randn(T, H, generator=g).to(torch.bfloat16)
+    w13 = (torch.randn(E, 2 * I, H, generator=g) * 0.2).to(torch.bfloat16)
+    w2 = (torch.randn(E, H, I, generator=g) * 0.2).to(torch.bfloat16)
+    logits = torch.randn(T, E, generator=g)
+    tw, ti, _ = O.fused_topk(x, logits, k, True)
+    got = O.fused_experts(x, w13, w2, tw, ti, mode="exact").float()
+    want = torch.zeros(T, H)
+    for t in range(T):
+        for j in range(k):
+            e = int(ti[t, j])
+            c1 = x[t].float() @ w13[e].float().t()
+            h = torch.nn.functional.silu(c1[:I]) * c1[I:]
+            want[t] += tw[t, j] * (h @ w2[e].float().t())
+    assert O.rel_l2(got, want) < 4e-3  # one bf16 rounding of the output
+    ref = O.fused_experts(x, w13, w2, tw, ti, mode="ref_rounding").float()
+    assert O.rel_l2(ref, want) < 2e-2
+
+
+@pytest.mark.parametrize("tp", [2, 4, 8])
+def test_tp_shards_sum_to_full_block(tp):
+    """Sum over ranks of block(I-slice) == block(full I): the sharding of layers/fused_moe.py:398-432."""
+    g = torch.Generator().manual_seed(1)
+    T, H, E, k, I = 12, 64, 8, 2, 128
+    x = torch.randn(T, H, generator=g).to(torch.bfloat16)
+    w13 = (torch.randn(E, 2 * I, H, generator=g) * 0.1).to(torch.bfloat16)
+    w2 = (torch.randn(E, H, I, generator=g) * 0.1).to(torch.bfloat16)
+    logits = torch.randn(T, E, generator=g)
+    tw, ti, _ = O.fused_topk(x, logits, k, True)
+    full = O.fused_experts(x, w13, w2, tw, ti, mode="exact").float()
+    parts = [O.fused_experts(x, *O.shard_expert_weights(w13, w2, tp, r), tw, ti, mode="exact").float()
+             for r in range(tp)]
+    assert O.rel_l2(sum(parts), full) < 6e-3
+    sh13, sh2 = O.shard_expert_weights(w13, w2, tp, 1)
+    assert sh13.shape == (E, 2 * I // tp, H) and sh2.shape == (E, H, I // tp)
+    assert torch.equal(sh13[:, :I // tp], w13[:, I // tp:2 * I // tp])
+    assert torch.equal(sh13[:, I // tp:], w13[:, I + I // tp:I + 2 * I // tp])
+
+
+def test_all_reduce_order_and_single_rounding():
+    a = torch.tensor([1.0, 256.0]).to(torch.bfloat16)
+    b = torch.tensor([2.0 ** -9, 1.0]).to(torch.bfloat16)
+    c = torch.tensor([2.0 ** -9, 1.0]).to(torch.bfloat16)
+    out = O.all_reduce([a, b, c])
+    # fp32 accumulation keeps the two small addends, a per-step bf16 rounding would lose them
+    assert out[0].item() == torch.tensor(1.0 + 2.0 ** -8).to(torch.bfloat16).item()
+    assert out[1].item() == 258.0
