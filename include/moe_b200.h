@@ -39,6 +39,10 @@ int moe_b200_abi_version(void);
 /* Token rows per grouped-GEMM tile = block size of the internal permutation (128). */
 int moe_b200_block_m(void);
 
+/* Number of kernels this library has launched in the calling process so far. No reference counterpart
+ * (the benchmark reports it). */
+uint64_t moe_b200_launch_count(void);
+
 /*
  * Router. Replaces ops.topk_softmax (csrc/ops.cpp:46-51, csrc/moe_topk_softmax_kernels.cu:476-503)
  * and, with renormalize != 0, the division in fused_topk (nanovllm/layers/for_moe/fused_moe.py:417-418).
@@ -93,6 +97,25 @@ int moe_b200_fused_experts(const void* x, const void* w13, const void* w2, const
                            const float* topk_weights, const int32_t* topk_ids, void* out, int T, int E, int top_k,
                            int H, int I, int activation, void* workspace, size_t workspace_bytes,
                            int32_t* status_word, void* stream);
+
+/*
+ * The two grouped GEMM passes on their own, for callers that keep the permutation (block size
+ * moe_b200_block_m()) and the intermediates themselves. Each replaces one invoke_fused_moe_kernel call
+ * of fused_experts_impl together with the element-wise kernel around it:
+ *   gate_up: for_moe/fused_moe.py:579-599 (GEMM + ops.silu_and_mul / swigluoai_and_mul). h_sorted is bf16
+ *            [rows_cap, I] in permuted order (row p belongs to flat index sorted_token_ids[p]); pad rows
+ *            are not written.
+ *   down:    for_moe/fused_moe.py:611-628 (GEMM with MUL_ROUTED_WEIGHT). c3 is bf16 [T*k, H] at flat index.
+ * rows_cap: rows of h_sorted = entries of sorted_token_ids, a multiple of 128.
+ */
+int moe_b200_grouped_gemm_gate_up(const void* x, const void* w13, const void* w13_bias, const int32_t* sorted_token_ids,
+                                  const int32_t* expert_ids, const int32_t* num_tokens_post_pad, void* h_sorted,
+                                  int rows_cap, int T, int E, int top_k, int H, int I, int activation,
+                                  int32_t* status_word, void* stream);
+int moe_b200_grouped_gemm_down(const void* h_sorted, int rows_cap, const void* w2, const void* w2_bias,
+                               const float* topk_weights, const int32_t* sorted_token_ids, const int32_t* expert_ids,
+                               const int32_t* num_tokens_post_pad, void* c3, int T, int E, int top_k, int H, int I,
+                               int32_t* status_word, void* stream);
 
 /*
  * Router + fused_experts in one call: what FusedMoE.forward runs on one rank before the

@@ -183,6 +183,7 @@ int launch_align_block_size(const int* topk_ids, int numel, int E, int block_siz
   if (numel <= kSmallNumel) {
     align_single_cta_kernel<<<1, kThreads, 0, stream>>>(topk_ids, numel, E, block_size, sorted_ids, sorted_cap,
                                                          expert_ids, expert_ids_cap, num_post_pad);
+    count_launches(1);
     return check_launch("moe_align_block_size");
   }
   if (workspace == nullptr || workspace_bytes < align_workspace_bytes(numel, E))
@@ -195,6 +196,7 @@ int launch_align_block_size(const int* topk_ids, int numel, int E, int block_siz
   align_scan_kernel<<<1, kThreads, 0, stream>>>(chunks, E, block_size, sorted_cap, expert_ids, expert_ids_cap,
                                                 num_post_pad, chunk_hist, cumsum);
   align_chunk_scatter_kernel<<<chunks, kThreads, 0, stream>>>(topk_ids, numel, E, chunk_hist, cumsum, sorted_ids);
+  count_launches(3);
   return check_launch("moe_align_block_size");
 }
 

@@ -317,6 +317,7 @@ int launch_ar(const Comm& c, const ArParams& p, bool oneshot, cudaStream_t strea
       return set_error(kStatusInvalidArgument, "custom allreduce only supports num gpus in (2,4,6,8). Actual num gpus = %d", c.world);
   }
 #undef MOE_B200_AR_CASE
+  count_launches(1);
   return check_launch("all_reduce");
 }
 

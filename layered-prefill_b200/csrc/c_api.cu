@@ -1,5 +1,6 @@
 // extern "C" layer of libmoe_b200 (declared in include/moe_b200.h): argument checks, workspace
 // carving and the launch sequence of the fused MoE block. No torch types, no allocation.
+#include <atomic>
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
@@ -29,6 +30,12 @@ int check_cuda(cudaError_t e, const char* what) {
 int check_launch(const char* what) { return check_cuda(cudaGetLastError(), what); }
 
 const char* last_error_string() { return g_error; }
+
+namespace {
+std::atomic<unsigned long long> g_launches{0};
+}
+void count_launches(int n) { g_launches.fetch_add(static_cast<unsigned long long>(n), std::memory_order_relaxed); }
+unsigned long long launch_count() { return g_launches.load(std::memory_order_relaxed); }
 
 namespace {
 
@@ -139,6 +146,43 @@ extern "C" {
 const char* moe_b200_last_error(void) { return last_error_string(); }
 int moe_b200_abi_version(void) { return 1; }
 int moe_b200_block_m(void) { return kBlockM; }
+uint64_t moe_b200_launch_count(void) { return launch_count(); }
+
+int moe_b200_grouped_gemm_gate_up(const void* x, const void* w13, const void* w13_bias, const int32_t* sorted_token_ids,
+                                  const int32_t* expert_ids, const int32_t* num_tokens_post_pad, void* h_sorted,
+                                  int rows_cap, int T, int E, int top_k, int H, int I, int activation,
+                                  int32_t* status_word, void* stream) {
+  if (int st = check_block_shapes(T, E, top_k, H, I)) return st;
+  if (x == nullptr || w13 == nullptr || sorted_token_ids == nullptr || expert_ids == nullptr ||
+      num_tokens_post_pad == nullptr || h_sorted == nullptr || status_word == nullptr)
+    return set_error(kStatusInvalidArgument, "grouped_gemm_gate_up: null pointer");
+  if (rows_cap % kBlockM != 0) return set_error(kStatusInvalidArgument, "grouped_gemm_gate_up: rows_cap must be a multiple of %d", kBlockM);
+  GroupedGemmArgs a{};
+  a.sorted_ids = sorted_token_ids; a.expert_ids = expert_ids; a.num_post_pad = num_tokens_post_pad;
+  a.numel = T * top_k; a.top_k = top_k; a.max_m_blocks = rows_cap / kBlockM; a.num_experts = E;
+  a.hidden = H; a.inter = I; a.activation = activation; a.act_alpha = 1.702f; a.act_limit = 7.0f; a.status = status_word;
+  return launch_grouped_gemm1(a, static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w13),
+                              static_cast<const __nv_bfloat16*>(w13_bias), static_cast<__nv_bfloat16*>(h_sorted),
+                              rows_cap, static_cast<cudaStream_t>(stream));
+}
+
+int moe_b200_grouped_gemm_down(const void* h_sorted, int rows_cap, const void* w2, const void* w2_bias,
+                               const float* topk_weights, const int32_t* sorted_token_ids, const int32_t* expert_ids,
+                               const int32_t* num_tokens_post_pad, void* c3, int T, int E, int top_k, int H, int I,
+                               int32_t* status_word, void* stream) {
+  if (int st = check_block_shapes(T, E, top_k, H, I)) return st;
+  if (h_sorted == nullptr || w2 == nullptr || topk_weights == nullptr || sorted_token_ids == nullptr ||
+      expert_ids == nullptr || num_tokens_post_pad == nullptr || c3 == nullptr || status_word == nullptr)
+    return set_error(kStatusInvalidArgument, "grouped_gemm_down: null pointer");
+  if (rows_cap % kBlockM != 0) return set_error(kStatusInvalidArgument, "grouped_gemm_down: rows_cap must be a multiple of %d", kBlockM);
+  GroupedGemmArgs a{};
+  a.sorted_ids = sorted_token_ids; a.expert_ids = expert_ids; a.num_post_pad = num_tokens_post_pad;
+  a.numel = T * top_k; a.top_k = top_k; a.max_m_blocks = rows_cap / kBlockM; a.num_experts = E;
+  a.hidden = H; a.inter = I; a.activation = 0; a.status = status_word;
+  return launch_grouped_gemm2(a, static_cast<const __nv_bfloat16*>(h_sorted), rows_cap,
+                              static_cast<const __nv_bfloat16*>(w2), static_cast<const __nv_bfloat16*>(w2_bias),
+                              topk_weights, static_cast<__nv_bfloat16*>(c3), static_cast<cudaStream_t>(stream));
+}
 
 int moe_b200_topk_softmax(const void* gating, int gating_is_bf16, float* topk_weights, int32_t* topk_ids,
                           int32_t* token_expert_indices, int T, int E, int k, int renormalize, void* stream) {

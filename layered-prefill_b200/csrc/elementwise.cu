@@ -96,6 +96,7 @@ int launch_silu_and_mul(__nv_bfloat16* out, const __nv_bfloat16* in, int rows, i
     silu_and_mul_kernel<<<grid_for(static_cast<long long>(rows) * (d / 8), 256), 256, 0, stream>>>(out, in, rows, d);
   else
     silu_and_mul_scalar_kernel<<<grid_for(static_cast<long long>(rows) * d, 256), 256, 0, stream>>>(out, in, rows, d);
+  count_launches(1);
   return check_launch("silu_and_mul");
 }
 
@@ -105,6 +106,7 @@ int launch_swigluoai_and_mul(__nv_bfloat16* out, const __nv_bfloat16* in, int ro
   if (rows == 0) return kStatusOk;
   swigluoai_and_mul_kernel<<<grid_for(static_cast<long long>(rows) * d, 256), 256, 0, stream>>>(out, in, rows, d, alpha,
                                                                                                 limit);
+  count_launches(1);
   return check_launch("swigluoai_and_mul");
 }
 
@@ -112,6 +114,7 @@ int launch_moe_sum(const __nv_bfloat16* in, __nv_bfloat16* out, int T, int k, in
   if (T < 0 || k <= 0 || H <= 0 || H % 8 != 0) return set_error(kStatusInvalidArgument, "moe_sum: H must be a multiple of 8");
   if (T == 0) return kStatusOk;
   moe_sum_kernel<<<grid_for(static_cast<long long>(T) * (H / 8), 256), 256, 0, stream>>>(in, out, T, k, H);
+  count_launches(1);
   return check_launch("moe_sum");
 }
 

@@ -463,6 +463,7 @@ int launch_grouped_gemm1(const GroupedGemmArgs& a, const __nv_bfloat16* x, const
   long long tiles = static_cast<long long>(a.max_m_blocks) * p.n_tiles;
   const int grid = static_cast<int>(tiles < device_sm_count() ? tiles : device_sm_count());
   grouped_gemm_kernel<1><<<grid, kThreadsGateUp, kSmemBytes, stream>>>(map_a, map_b, p);
+  count_launches(1);
   return check_launch("grouped_gemm gate_up");
 }
 
@@ -496,6 +497,7 @@ int launch_grouped_gemm2(const GroupedGemmArgs& a, const __nv_bfloat16* h_sorted
   long long tiles = static_cast<long long>(a.max_m_blocks) * p.n_tiles;
   const int grid = static_cast<int>(tiles < device_sm_count() ? tiles : device_sm_count());
   grouped_gemm_kernel<2><<<grid, kThreadsDown, kSmemBytes, stream>>>(map_a, map_b, p);
+  count_launches(1);
   return check_launch("grouped_gemm down");
 }
 

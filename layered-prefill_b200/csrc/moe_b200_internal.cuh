@@ -26,6 +26,9 @@ int set_error(int status, const char* fmt, ...);
 int check_launch(const char* what);
 int check_cuda(cudaError_t e, const char* what);
 const char* last_error_string();
+// Host-side count of kernels this library has launched in this process (reported by the benchmark).
+void count_launches(int n);
+unsigned long long launch_count();
 
 constexpr int kBlockM = 128;  // token rows per grouped-GEMM tile (and the internal permutation block)
 

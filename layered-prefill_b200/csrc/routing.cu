@@ -244,6 +244,7 @@ int launch_topk_softmax(const void* gating, int gating_is_bf16, float* topk_w, i
       }
     }
   }
+  count_launches(1);
   return check_launch("topk_softmax");
 }
 
