@@ -141,18 +141,22 @@ def fused_experts(hidden_states: torch.Tensor, w1: torch.Tensor, w2: torch.Tenso
 def fused_moe_forward(hidden_states: torch.Tensor, router_logits: torch.Tensor, w13: torch.Tensor, w2: torch.Tensor,
                       top_k: int, renormalize: bool = True, activation: str = "silu", inplace: bool = True,
                       w13_bias: Optional[torch.Tensor] = None, w2_bias: Optional[torch.Tensor] = None,
-                      comm=None) -> torch.Tensor:
+                      comm=None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Router + experts (+ tensor-parallel reduction when `comm` is an initialised CustomAllreduce) through
     one library call: what FusedMoE.forward followed by maybe_all_reduce_tensor_model_parallel does
-    (nanovllm/layers/fused_moe.py:746-787, nanovllm/models/qwen3_moe.py:99-116)."""
-    _check_experts_args(hidden_states, w13, w2, router_logits[:, :top_k], router_logits[:, :top_k], activation)
+    (nanovllm/layers/fused_moe.py:746-787, nanovllm/models/qwen3_moe.py:99-116). `out` (bf16 [T, H]) is used
+    as the destination when given; otherwise the result overwrites hidden_states (inplace) or a new tensor."""
     T, H = hidden_states.shape
     E, two_i, _ = w13.shape
     inter = two_i // 2
-    assert router_logits.shape == (T, E)
+    assert router_logits.shape == (T, E), "router_logits must be [tokens, experts]"
+    _check_experts_args(hidden_states, w13, w2, router_logits, router_logits, activation)
     logits = router_logits if router_logits.dtype in (torch.bfloat16, torch.float32) else router_logits.float()
     logits = logits.contiguous()
-    out = hidden_states if inplace else torch.empty_like(hidden_states)
+    if out is None:
+        out = hidden_states if inplace else torch.empty_like(hidden_states)
+    else:
+        assert out.shape == hidden_states.shape and out.dtype == hidden_states.dtype and out.is_contiguous()
     if T == 0:
         return out
     dev = hidden_states.device
