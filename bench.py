@@ -134,6 +134,7 @@ def build_parser():
     ap.add_argument("--workload", default="decode")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--weight-sets", type=int, default=4, help="distinct weight copies rotated through (L2 defeat)")
+    ap.add_argument("--tokens", type=int, default=None, help="override the workload's token count (profiling)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     return ap
@@ -203,6 +204,8 @@ def main():
     if name not in W.WORKLOADS:
         raise SystemExit(f"unknown workload {args.workload}; known: {sorted(W.WORKLOADS)} or {sorted(ALIASES)}")
     wl = W.WORKLOADS[name]
+    if args.tokens is not None:
+        wl = W.with_tokens(wl, args.tokens)
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))

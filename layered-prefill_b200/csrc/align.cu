@@ -145,11 +145,19 @@ align_scan_kernel(int num_chunks, int E, int block_size, int sorted_cap, int* __
   __shared__ int total_smem;
   int run = 0;
   if (threadIdx.x < E) {
-    for (int c = 0; c < num_chunks; ++c) {
-      const size_t at = static_cast<size_t>(c) * E + threadIdx.x;
-      const int n = chunk_hist[at];
-      chunk_hist[at] = run;  // exclusive prefix over chunks: first slot (within the expert) of chunk c
-      run += n;
+    // exclusive prefix over chunks: chunk_hist[c][e] becomes the first slot (within the expert) of
+    // chunk c. Loads go out in batches of 16 before the stores, so their latencies overlap.
+    constexpr int kBatch = 16;
+    for (int c0 = 0; c0 < num_chunks; c0 += kBatch) {
+      int n[kBatch];
+#pragma unroll
+      for (int u = 0; u < kBatch; ++u)
+        n[u] = c0 + u < num_chunks ? chunk_hist[static_cast<size_t>(c0 + u) * E + threadIdx.x] : 0;
+#pragma unroll
+      for (int u = 0; u < kBatch; ++u) {
+        if (c0 + u < num_chunks) chunk_hist[static_cast<size_t>(c0 + u) * E + threadIdx.x] = run;
+        run += n[u];
+      }
     }
   }
   const int start = scan_and_publish(run, E, block_size, sorted_cap, expert_ids_cap, expert_ids, num_post_pad,

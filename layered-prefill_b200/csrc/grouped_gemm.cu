@@ -17,7 +17,9 @@
 //     reference's three bf16 roundings and only h is written, in permuted order;
 //   * pass 2 scales by the routed weight and writes bf16 rows at their flat index t*k+j.
 // The tile list is static: tile = blockIdx.x + i*gridDim.x over (m_block, n_tile), n fastest.
+#include <cmath>
 #include <cstdio>
+#include <cstring>
 
 #include "act_math.cuh"
 #include "moe_b200_internal.cuh"
@@ -30,15 +32,14 @@ namespace {
 constexpr int BM = kBlockM;
 constexpr int BK = 64;  // bf16 elements per K block = one 128-byte swizzle row
 constexpr int kUmmaK = 16;
-constexpr int kStages = 4;
+constexpr int kMaxStages = 8;
 constexpr int kMaxBN = 256;
 constexpr int kABytes = BM * BK * 2;
-constexpr int kBBytes = kMaxBN * BK * 2;
-constexpr int kStageBytes = kABytes + kBBytes;
 constexpr int kAccCols = 256;
 constexpr int kTmemCols = 512;
-constexpr int kGatherLookahead = 2;
-constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr int kBarrierBytes = 1024;                      // barriers + TMEM slot, in front of the ring
+constexpr int kSmemLimit = 227 * 1024;                   // opt-in shared memory per CTA on sm_100
+constexpr int kRingBudget = kSmemLimit - kBarrierBytes - 1024 /*alignment slack*/;
 
 constexpr int kWarpTma = 0;
 constexpr int kWarpMma = 1;
@@ -67,6 +68,8 @@ struct KernelParams {
   const __nv_bfloat16* bias;  // [E, 2*inter] (gate_up) or [E, hidden] (down), may be null
   float alpha, limit;
   int* status;
+  int stages;       // ring depth (2..kMaxStages)
+  int stage_bytes;  // kABytes + mma_n * 128
 };
 
 union Pack8 {
@@ -83,17 +86,20 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   extern __shared__ uint8_t smem_raw[];
   // operand stages want 1024-byte alignment in the shared window (swizzle atoms, descriptor base offset 0)
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-  uint64_t* bar_full = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
-  uint64_t* bar_empty = bar_full + kStages;
-  uint64_t* bar_tmem_full = bar_empty + kStages;
+  uint64_t* bar_full = reinterpret_cast<uint64_t*>(smem);
+  uint64_t* bar_empty = bar_full + kMaxStages;
+  uint64_t* bar_tmem_full = bar_empty + kMaxStages;
   uint64_t* bar_tmem_empty = bar_tmem_full + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_tmem_empty + 2);
+  uint8_t* ring = smem + kBarrierBytes;
+  const uint32_t num_stages = static_cast<uint32_t>(p.stages);
+  const uint32_t stage_bytes = static_cast<uint32_t>(p.stage_bytes);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kStages; ++s) {
+    for (int s = 0; s < kMaxStages; ++s) {
       mbar_init(&bar_full[s], kMode == 1 ? 1 + 128 : 1);
       mbar_init(&bar_empty[s], 1);
     }
@@ -120,19 +126,17 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 
   if (warp == kWarpTma) {
     // ------------------------------------------------------------------ TMA producer
-    uint32_t it = 0;
+    uint32_t s = 0, ph = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
       const int m_blk = tile / p.n_tiles;
       const int n0 = (tile % p.n_tiles) * p.tile_cols;
       const int e = p.expert_ids[m_blk];
-      for (int kb = 0; kb < num_kb; ++kb, ++it) {
+      for (int kb = 0; kb < num_kb; ++kb) {
         if (lane == 0) {
-          const uint32_t s = it % kStages;
-          const uint32_t ph = (it / kStages) & 1u;
           ok = mbar_wait(&bar_empty[s], ph ^ 1u);
           if (ok) {
-            uint8_t* a_dst = smem + s * kStageBytes;
+            uint8_t* a_dst = ring + s * stage_bytes;
             uint8_t* b_dst = a_dst + kABytes;
             if (kMode == 1) {
               mbar_arrive_expect_tx(&bar_full[s], static_cast<uint32_t>(p.mma_n) * 128u);
@@ -153,12 +157,16 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         }
         ok = __shfl_sync(0xffffffffu, ok, 0);
         if (!ok) break;
+        if (++s == num_stages) {
+          s = 0;
+          ph ^= 1u;
+        }
       }
     }
   } else if (warp == kWarpMma) {
     // ------------------------------------------------------------------ MMA issuer
     const uint32_t idesc = umma_idesc_bf16(BM, static_cast<uint32_t>(p.mma_n));
-    uint32_t it = 0;
+    uint32_t s = 0, ph = 0;
     uint32_t tile_iter = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tile_iter) {
@@ -172,14 +180,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       if (!ok) break;
       tc_fence_after_sync();
       const uint32_t d_tmem = tmem_base + acc * kAccCols;
-      for (int kb = 0; kb < num_kb; ++kb, ++it) {
+      for (int kb = 0; kb < num_kb; ++kb) {
         if (lane == 0) {
-          const uint32_t s = it % kStages;
-          const uint32_t ph = (it / kStages) & 1u;
           ok = mbar_wait(&bar_full[s], ph);
           if (ok) {
             tc_fence_after_sync();
-            const uint32_t a_addr = smem_u32(smem + s * kStageBytes);
+            const uint32_t a_addr = smem_u32(ring + s * stage_bytes);
             const uint64_t adesc = umma_desc_k_sw128(a_addr);
             const uint64_t bdesc = umma_desc_k_sw128(a_addr + kABytes);
 #pragma unroll
@@ -194,6 +200,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         }
         ok = __shfl_sync(0xffffffffu, ok, 0);
         if (!ok) break;
+        if (++s == num_stages) {
+          s = 0;
+          ph ^= 1u;
+        }
       }
       if (ok && lane == 0) umma_commit(&bar_tmem_full[acc]);
       __syncwarp();
@@ -307,7 +317,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     const int ch = lane & 7;             // 16-byte chunk inside the 128-byte row
     const int row0 = gw * 4 + sub;       // rows handled: row0 + 16*i
     const uint32_t swz = static_cast<uint32_t>((ch ^ (row0 & 7)) << 4);
-    uint32_t it = 0;
+    uint32_t s = 0, ph = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
       const int m_blk = tile / p.n_tiles;
@@ -317,16 +327,14 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         const int flat = p.sorted_ids[static_cast<long long>(m_blk) * BM + row0 + 16 * i];
         src[i] = flat < p.numel ? p.x + static_cast<long long>(flat / p.top_k) * p.K + ch * 8 : nullptr;
       }
-      for (int kb = 0; kb < num_kb; ++kb, ++it) {
-        const uint32_t s = it % kStages;
-        const uint32_t ph = (it / kStages) & 1u;
+      for (int kb = 0; kb < num_kb; ++kb) {
         ok = mbar_wait(&bar_empty[s], ph ^ 1u);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) {
           if (lane == 0) report(p.status, kErrWaitEmpty);
           break;
         }
-        const uint32_t a_base = smem_u32(smem + s * kStageBytes);
+        const uint32_t a_base = smem_u32(ring + s * stage_bytes);
         const bool in_k = kb * BK + ch * 8 < p.K;
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
@@ -335,20 +343,15 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           cp_async_16(dst, live ? static_cast<const void*>(src[i] + kb * BK) : static_cast<const void*>(p.x),
                       live ? 16u : 0u);
         }
-        cp_async_commit();
-        if (it >= kGatherLookahead) {
-          cp_async_wait<kGatherLookahead>();
-          fence_proxy_async_smem();
-          mbar_arrive(&bar_full[(it - kGatherLookahead) % kStages]);
+        // the stage's barrier counts this thread as arrived once the copies above have landed
+        cp_async_mbar_arrive_noinc(&bar_full[s]);
+        if (++s == num_stages) {
+          s = 0;
+          ph ^= 1u;
         }
       }
     }
-    cp_async_wait<0>();
-    fence_proxy_async_smem();
-    if (ok) {
-      for (uint32_t j = it >= kGatherLookahead ? it - kGatherLookahead : 0; j < it; ++j)
-        mbar_arrive(&bar_full[j % kStages]);
-    }
+    cp_async_wait_all();
   }
 
   tc_fence_before_sync();
@@ -402,17 +405,56 @@ template <int kMode>
 int ensure_smem_attr() {
   static bool done = false;
   if (!done) {
-    const cudaError_t e = cudaFuncSetAttribute(grouped_gemm_kernel<kMode>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    const cudaError_t e = cudaFuncSetAttribute(grouped_gemm_kernel<kMode>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit);
     if (e != cudaSuccess) return check_cuda(e, "cudaFuncSetAttribute(grouped_gemm_kernel)");
     done = true;
   }
   return kStatusOk;
 }
 
-int pick_gate_up_tile(int inter) {
+// Token blocks the permutation is expected to produce: experts hit at least once (each token picks
+// top_k distinct experts out of E) plus the full blocks of the busy ones. Only used to pick tile widths.
+double expected_m_blocks(int numel, int top_k, int num_experts) {
+  const double tokens = static_cast<double>(numel) / top_k;
+  const double miss = pow(1.0 - static_cast<double>(top_k) / num_experts, tokens);
+  return num_experts * (1.0 - miss) + static_cast<double>(numel) / BM;
+}
+
+// Fraction of SM-time doing work when `tiles` equal tiles are dealt round-robin to `sms` persistent CTAs.
+double wave_efficiency(double tiles, int sms) {
+  const double waves = ceil(tiles / sms);
+  return waves > 0 ? tiles / (waves * sms) : 1.0;
+}
+
+// Widest gate_up tile (output columns, a multiple of 16 dividing `inter`) among those within 2 % of the
+// best wave efficiency: for decode-sized batches the tile count is a handful of waves, and a width that
+// leaves the last wave nearly empty costs more than the narrower MMA.
+int pick_gate_up_tile(int inter, double m_blocks) {
+  const int sms = device_sm_count();
+  double best = 0.0;
+  for (int c = 128; c >= 16; c -= 16)
+    if (inter % c == 0 && (c >= 64 || inter < 64)) best = fmax(best, wave_efficiency(m_blocks * (inter / c), sms));
+  for (int c = 128; c >= 16; c -= 16)
+    if (inter % c == 0 && (c >= 64 || inter < 64) && wave_efficiency(m_blocks * (inter / c), sms) >= best - 0.02) return c;
   for (int c = 128; c >= 16; c -= 16)
     if (inter % c == 0) return c;
   return 0;
+}
+
+int pick_down_tile(int hidden, double m_blocks) {
+  if (hidden <= 128) return (hidden + 15) / 16 * 16;
+  const int sms = device_sm_count();
+  const double e256 = wave_efficiency(m_blocks * ((hidden + 255) / 256), sms);
+  const double e128 = wave_efficiency(m_blocks * ((hidden + 127) / 128), sms);
+  return e256 >= e128 - 0.02 ? 256 : 128;
+}
+
+// Ring depth that fits the shared-memory budget for a given accumulator width.
+void pick_ring(int mma_n, int* stages, int* stage_bytes) {
+  *stage_bytes = kABytes + mma_n * 128;
+  int s = kRingBudget / *stage_bytes;
+  if (s > kMaxStages) s = kMaxStages;
+  *stages = s;
 }
 
 int check_common(const GroupedGemmArgs& a) {
@@ -441,7 +483,7 @@ int launch_grouped_gemm1(const GroupedGemmArgs& a, const __nv_bfloat16* x, const
                          const __nv_bfloat16* w13_bias, __nv_bfloat16* h_sorted, int rows_cap, cudaStream_t stream) {
   if (int st = check_common(a)) return st;
   if (a.numel == 0 || a.max_m_blocks == 0) return kStatusOk;
-  const int tile_cols = pick_gate_up_tile(a.inter);
+  const int tile_cols = pick_gate_up_tile(a.inter, expected_m_blocks(a.numel, a.top_k, a.num_experts));
   const int mma_n = 2 * tile_cols;
   if (int st = ensure_smem_attr<1>()) return st;
 
@@ -458,11 +500,13 @@ int launch_grouped_gemm1(const GroupedGemmArgs& a, const __nv_bfloat16* x, const
   p.interleaved = a.activation == 1 ? 1 : 0;
   p.out = h_sorted; p.out_ld = a.inter; p.topk_w = nullptr; p.bias = w13_bias;
   p.alpha = a.act_alpha; p.limit = a.act_limit; p.status = a.status;
+  pick_ring(mma_n, &p.stages, &p.stage_bytes);
   (void)rows_cap;
 
   long long tiles = static_cast<long long>(a.max_m_blocks) * p.n_tiles;
   const int grid = static_cast<int>(tiles < device_sm_count() ? tiles : device_sm_count());
-  grouped_gemm_kernel<1><<<grid, kThreadsGateUp, kSmemBytes, stream>>>(map_a, map_b, p);
+  const int smem_bytes = kBarrierBytes + 1024 + p.stages * p.stage_bytes;
+  grouped_gemm_kernel<1><<<grid, kThreadsGateUp, smem_bytes, stream>>>(map_a, map_b, p);
   count_launches(1);
   return check_launch("grouped_gemm gate_up");
 }
@@ -473,9 +517,7 @@ int launch_grouped_gemm2(const GroupedGemmArgs& a, const __nv_bfloat16* h_sorted
   if (int st = check_common(a)) return st;
   if (a.numel == 0 || a.max_m_blocks == 0) return kStatusOk;
   if (a.hidden % 16 != 0) return set_error(kStatusInvalidArgument, "grouped GEMM down: hidden must be a multiple of 16");
-  // 256-column tiles once there is more than one token block per expert on average, else 128.
-  int tile_cols = a.max_m_blocks > 2 * a.num_experts ? 256 : 128;
-  if (a.hidden < tile_cols) tile_cols = (a.hidden + 15) / 16 * 16;
+  const int tile_cols = pick_down_tile(a.hidden, expected_m_blocks(a.numel, a.top_k, a.num_experts));
   if (int st = ensure_smem_attr<2>()) return st;
 
   CUtensorMap map_a, map_b;
@@ -493,10 +535,12 @@ int launch_grouped_gemm2(const GroupedGemmArgs& a, const __nv_bfloat16* h_sorted
   p.out_cols = a.hidden; p.inter = a.inter; p.interleaved = 0;
   p.out = c3; p.out_ld = a.hidden; p.topk_w = topk_w; p.bias = w2_bias;
   p.alpha = 0.f; p.limit = 0.f; p.status = a.status;
+  pick_ring(p.mma_n, &p.stages, &p.stage_bytes);
 
   long long tiles = static_cast<long long>(a.max_m_blocks) * p.n_tiles;
   const int grid = static_cast<int>(tiles < device_sm_count() ? tiles : device_sm_count());
-  grouped_gemm_kernel<2><<<grid, kThreadsDown, kSmemBytes, stream>>>(map_a, map_b, p);
+  const int smem_bytes = kBarrierBytes + 1024 + p.stages * p.stage_bytes;
+  grouped_gemm_kernel<2><<<grid, kThreadsDown, smem_bytes, stream>>>(map_a, map_b, p);
   count_launches(1);
   return check_launch("grouped_gemm down");
 }

@@ -89,7 +89,15 @@ topk_softmax_pow2_kernel(const void* __restrict__ gating, float* __restrict__ to
 #pragma unroll
   for (int ii = 0; ii < VPT; ++ii) v[ii] = v[ii] * inv_sum;
 
-  float picked_sum = 0.f;
+  // Winner number k_idx is kept in registers by lane k_idx % TPR of the row's group (slot k_idx / TPR),
+  // so the results leave the kernel as one store per lane and nothing is read back from memory.
+  float keep_w[VPT];
+  int keep_id[VPT];
+#pragma unroll
+  for (int s = 0; s < VPT; ++s) {
+    keep_w[s] = 0.f;
+    keep_id[s] = 0;
+  }
   for (int k_idx = 0; k_idx < k; ++k_idx) {
     float best = v[0];
     int expert = first_col;
@@ -113,24 +121,47 @@ topk_softmax_pow2_kernel(const void* __restrict__ gating, float* __restrict__ to
         expert = other_expert;
       }
     }
-    if (g == 0 && row_ok) {
-      const size_t idx = static_cast<size_t>(k) * row + k_idx;
-      topk_w[idx] = best;
-      topk_ids[idx] = expert;
-      if (token_expert_indices != nullptr) token_expert_indices[idx] = k_idx * num_rows + row;
-      picked_sum += best;
+    if (g == k_idx % TPR) {
+      const int slot = k_idx / TPR;
+#pragma unroll
+      for (int s = 0; s < VPT; ++s) {
+        if (s == slot) {
+          keep_w[s] = best;
+          keep_id[s] = expert;
+        }
+      }
     }
     if (k_idx + 1 < k) {
       const int ldg_group = expert / S::kColsPerGroupLdg;
       const int owner = (expert / ELTS) % TPR;
-      if (g == owner) v[ldg_group * ELTS + expert % ELTS] = -10000.f;
+      const int at = ldg_group * ELTS + expert % ELTS;
+      if (g == owner) {
+#pragma unroll
+        for (int s = 0; s < VPT; ++s)
+          if (s == at) v[s] = -10000.f;
+      }
     }
   }
 
-  if (renormalize && g == 0 && row_ok) {
-    for (int k_idx = 0; k_idx < k; ++k_idx) {
-      const size_t idx = static_cast<size_t>(k) * row + k_idx;
-      topk_w[idx] = topk_w[idx] / picked_sum;
+  float inv_picked = 1.f;
+  if (renormalize) {
+    float picked_sum = 0.f;
+#pragma unroll
+    for (int s = 0; s < VPT; ++s) picked_sum += keep_w[s];
+#pragma unroll
+    for (int mask = TPR / 2; mask > 0; mask /= 2) picked_sum += __shfl_xor_sync(0xffffffffu, picked_sum, mask, TPR);
+    inv_picked = picked_sum;
+  }
+  if (row_ok) {
+#pragma unroll
+    for (int s = 0; s < VPT; ++s) {
+      const int k_idx = s * TPR + g;
+      if (k_idx < k) {
+        const size_t idx = static_cast<size_t>(k) * row + k_idx;
+        topk_w[idx] = renormalize ? keep_w[s] / inv_picked : keep_w[s];
+        topk_ids[idx] = keep_id[s];
+        if (token_expert_indices != nullptr) token_expert_indices[idx] = k_idx * num_rows + row;
+      }
     }
   }
 }
