@@ -1,0 +1,112 @@
+"""Worker of the multi-GPU tests: one process per GPU (torch.distributed.run), NCCL for bootstrap only.
+
+Checks, on every rank, against the CPU oracle:
+  1. plain peer-memory all-reduce (one-shot and two-shot, staged and registered input) on several sizes;
+  2. the fused k-slot-sum + all-reduce;
+  3. the whole tensor-parallel MoE block (I sharded as the reference's weight_loader does).
+Prints "TP_WORKER_OK rank=<r>" on success; any failure raises.
+"""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, ROOT)
+
+
+def main():
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    rank = int(os.environ["RANK"])
+    world = int(os.environ["WORLD_SIZE"])
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", device_id=dev)
+    from layered_prefill_b200 import fused_moe, ops
+    from layered_prefill_b200.custom_all_reduce import CustomAllreduce
+    from layered_prefill_b200.layer import FusedMoE
+    from oracle import moe_oracle as O
+
+    comm = CustomAllreduce(group=dist.new_group(backend="gloo"), device=dev)
+    assert not comm.disabled, "peer-memory all-reduce did not initialise"
+
+    # ---- 1. plain all-reduce
+    for numel in (8, 2048, 64 * 2048, 256 * 2048 + 8, 3 * 1024 * 1024):
+        for dtype in (torch.bfloat16, torch.float32):
+            for algo in (1, 2):
+                parts = []
+                for r in range(world):
+                    g = torch.Generator().manual_seed(numel + 17 * r)
+                    parts.append(torch.randn(numel, generator=g).to(dtype))
+                want = O.all_reduce(parts)
+                mine = parts[rank].to(dev)
+                out = comm.all_reduce(mine, registered=False, algo=algo)
+                torch.cuda.synchronize()
+                assert torch.equal(out.cpu(), want), f"all_reduce numel={numel} {dtype} algo={algo}"
+    # default dispatch through the reference-shaped entry
+    t = torch.full((64, 2048), float(rank + 1), dtype=torch.bfloat16, device=dev)
+    got = comm.custom_all_reduce(t)
+    assert got is not None and torch.all(got == sum(range(1, world + 1)))
+    assert ops.read_status(dev) == 0
+
+    # ---- 2. fused k-slot sum + all-reduce (both algorithms)
+    from layered_prefill_b200._lib import check, lib
+    for T, k, H, algo in ((64, 8, 2048, 1), (64, 8, 2048, 2), (300, 4, 512, 2), (1, 2, 64, 1)):
+        c3s = []
+        for r in range(world):
+            g = torch.Generator().manual_seed(T * 7 + r)
+            c3s.append(torch.randn(T, k, H, generator=g).to(torch.bfloat16))
+        want = O.all_reduce([O.moe_sum(c) for c in c3s])
+        c3 = c3s[rank].to(dev)
+        out = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
+        check(lib.moe_b200_ar_moe_sum_all_reduce(comm._ptr, c3.data_ptr(), out.data_ptr(), T, k, H,
+                                                 comm.buffer_ptrs[rank], comm.max_size, algo,
+                                                 ops.status_word(dev).data_ptr(),
+                                                 torch.cuda.current_stream().cuda_stream))
+        torch.cuda.synchronize()
+        assert torch.equal(out.cpu(), want), f"moe_sum_all_reduce T={T} algo={algo}"
+    assert ops.read_status(dev) == 0
+
+    # ---- 3. whole block, tensor parallel, through the FusedMoE mirror
+    g = torch.Generator().manual_seed(5)
+    T, H, E, k, I = 96, 512, 16, 4, 64 * world
+    x = torch.randn(T, H, generator=g).to(torch.bfloat16)
+    w13 = (torch.randn(E, 2 * I, H, generator=g) * 0.05).to(torch.bfloat16)
+    w2 = (torch.randn(E, H, I, generator=g) * 0.05).to(torch.bfloat16)
+    logits = torch.randn(T, E, generator=g).to(torch.bfloat16)
+    want = O.moe_block_tp(x, logits, w13, w2, k, world)
+    layer = FusedMoE(E, k, H, I, params_dtype=torch.bfloat16, reduce_results=True).to(dev)
+    assert layer.tp_size == world and layer.intermediate_size_per_partition == I // world
+    for e in range(E):  # checkpoint tensors are per expert: gate, up, down
+        layer.weight_loader(layer.w13_weight, w13[e, :I].to(dev), "experts.w13_weight", "w1", e)
+        layer.weight_loader(layer.w13_weight, w13[e, I:].to(dev), "experts.w13_weight", "w3", e)
+        layer.weight_loader(layer.w2_weight, w2[e].to(dev), "experts.w2_weight", "w2", e)
+    sh13, sh2 = O.shard_expert_weights(w13, w2, world, rank)
+    assert torch.equal(layer.w13_weight.cpu(), sh13) and torch.equal(layer.w2_weight.cpu(), sh2)
+    import layered_prefill_b200.custom_all_reduce as car
+    car._ar_comm = comm
+    out = layer(x.to(dev).clone(), logits.to(dev))
+    torch.cuda.synchronize()
+    assert ops.read_status(dev) == 0
+    rl, ma = O.rel_l2(out.cpu(), want), O.max_abs(out.cpu(), want)
+    assert rl <= 5e-3 and ma <= 2e-2, (rl, ma)
+    # every rank holds identical bits
+    gathered = [torch.empty_like(out) for _ in range(world)]
+    dist.all_gather(gathered, out)
+    assert all(torch.equal(gathered[0], t) for t in gathered)
+    # unfused route: forward (no reduction) then the reference-shaped all-reduce call
+    layer.reduce_results = False
+    part = layer(x.to(dev).clone(), logits.to(dev))
+    red = layer.maybe_all_reduce_tensor_model_parallel(part)
+    assert torch.equal(red, out)
+
+    dist.barrier()
+    comm.close()
+    dist.destroy_process_group()
+    print(f"TP_WORKER_OK rank={rank}", flush=True)
+
+
+if __name__ == "__main__":
+    main()
