@@ -67,6 +67,32 @@ int moe_b200_moe_align_block_size(const int32_t* topk_ids, int numel, int E, int
                                   int32_t* num_tokens_post_pad, void* workspace, size_t workspace_bytes, void* stream);
 
 /*
+ * The same permutation for callers that cannot hand over a workspace because they have no way to
+ * allocate one. This entry point has no counterpart in the reference. It exists for hosts that bind the
+ * reference's exact op signature (which carries no workspace argument) but, unlike the reference's op,
+ * must not allocate inside the call: a serving engine that gave every free byte of device memory to
+ * its KV-cache pool at start-up, or a hot path on which touching the CUDA allocator (and the implicit
+ * synchronisation a cudaMalloc/cudaFree can bring) is not acceptable. The per-chunk histogram and the
+ * cumsum table live in an array built into the library image instead; every GPU that loads the library
+ * holds those moe_b200_moe_align_static_scratch_bytes() bytes (130 KiB) until the process exits.
+ *
+ * Limit: ceil(numel / 1024) * E + E + 1 <= 33280 words, e.g. 131072 flat indices (16384 tokens with
+ * top-8) for up to 256 experts. Larger requests fail with MOE_B200_TOO_LARGE and a message; nothing is
+ * launched then. Outputs and their sizes are exactly those of moe_b200_moe_align_block_size.
+ *
+ * The call performs no cudaMalloc, cudaFree or other allocating call. The first call on each device looks
+ * up the device address of the built-in array (cudaGetSymbolAddress, with that device current); make that
+ * first call outside of any stream capture. All calls on a device share the one array, which keeps
+ * whatever the last call left in it; nothing in it needs clearing between calls, because each call writes
+ * every word before reading it. Two calls that can overlap on the GPU (different streams, no ordering
+ * between them) race on the array and give undefined results: order them.
+ */
+size_t moe_b200_moe_align_static_scratch_bytes(void);
+int moe_b200_moe_align_block_size_static(const int32_t* topk_ids, int numel, int E, int block_size,
+                                         int32_t* sorted_token_ids, int sorted_cap, int32_t* expert_ids,
+                                         int expert_ids_cap, int32_t* num_tokens_post_pad, void* stream);
+
+/*
  * Stand-alone gated activations on bf16. Replace ops.silu_and_mul / ops.swigluoai_and_mul
  * (csrc/ops.cpp:29-36, csrc/activation_kernels.cu:68-109). in: [rows, 2d], out: [rows, d].
  */

@@ -53,6 +53,8 @@ SIGNATURES = {
     "moe_b200_topk_softmax": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
     "moe_b200_align_workspace_bytes": (c_size_t, [c_int, c_int]),
     "moe_b200_moe_align_block_size": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_size_t, c_void_p]),
+    "moe_b200_moe_align_static_scratch_bytes": (c_size_t, []),
+    "moe_b200_moe_align_block_size_static": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p]),
     "moe_b200_silu_and_mul": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p]),
     "moe_b200_swigluoai_and_mul": (c_int, [c_void_p, c_void_p, c_int, c_int, c_float, c_float, c_void_p]),
     "moe_b200_moe_sum": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),

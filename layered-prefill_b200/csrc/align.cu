@@ -208,4 +208,50 @@ int launch_align_block_size(const int* topk_ids, int numel, int E, int block_siz
   return check_launch("moe_align_block_size");
 }
 
+// ---------------------------------------------------------------- allocation-free variant
+// Same three kernels, with the per-chunk histogram and the cumsum table in a fixed array that lives in
+// the library image instead of in memory the caller had to allocate. Every GPU that loads the library
+// carries these kStaticScratchInts * 4 bytes (130 KiB) until the process exits.
+constexpr int kStaticScratchInts = 33280;  // e.g. 128 chunks (131072 flat indices) x 256 experts + 257
+static __device__ __align__(256) int g_align_scratch[kStaticScratchInts];
+
+int static_align_scratch_ints() { return kStaticScratchInts; }
+
+int launch_align_block_size_static(const int* topk_ids, int numel, int E, int block_size, int* sorted_ids,
+                                   int sorted_cap, int* expert_ids, int expert_ids_cap, int* num_post_pad,
+                                   cudaStream_t stream) {
+  if (E <= 0 || E > kMaxExperts) return set_error(kStatusInvalidArgument, "moe_align_block_size_static: 1..1024 experts");
+  if (block_size <= 0 || numel < 0) return set_error(kStatusInvalidArgument, "moe_align_block_size_static: bad sizes");
+  const int chunks = numel > 0 ? (numel + kThreads - 1) / kThreads : 1;
+  const long long need = static_cast<long long>(chunks) * E + E + 1;
+  if (need > kStaticScratchInts)
+    return set_error(kStatusTooLarge,
+                     "moe_align_block_size_static: %d flat indices x %d experts need %lld scratch words, the built-in "
+                     "scratch holds %d (use moe_b200_moe_align_block_size with a caller workspace)",
+                     numel, E, need, kStaticScratchInts);
+  // In host code g_align_scratch is only a handle for the symbol; the address kernels can use has to be
+  // asked for, once per device, while that device is current.
+  static int* scratch_of_device[64] = {nullptr};
+  int dev = 0;
+  if (int st = check_cuda(cudaGetDevice(&dev), "cudaGetDevice")) return st;
+  if (dev < 0 || dev >= 64) return set_error(kStatusInvalidArgument, "moe_align_block_size_static: device index %d", dev);
+  if (scratch_of_device[dev] == nullptr) {
+    int* ptr = nullptr;
+    if (int st = check_cuda(cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_align_scratch),
+                            "cudaGetSymbolAddress(g_align_scratch)"))
+      return st;
+    scratch_of_device[dev] = ptr;
+  }
+  int* chunk_hist = scratch_of_device[dev];
+  int* cumsum = chunk_hist + static_cast<size_t>(chunks) * E;
+  // Nothing in the scratch has to start at zero: the histogram kernel writes every chunk_hist word of
+  // this call and the scan kernel every cumsum word before anything reads them.
+  align_chunk_hist_kernel<<<chunks, kThreads, 0, stream>>>(topk_ids, numel, E, sorted_ids, sorted_cap, chunk_hist);
+  align_scan_kernel<<<1, kThreads, 0, stream>>>(chunks, E, block_size, sorted_cap, expert_ids, expert_ids_cap,
+                                                num_post_pad, chunk_hist, cumsum);
+  align_chunk_scatter_kernel<<<chunks, kThreads, 0, stream>>>(topk_ids, numel, E, chunk_hist, cumsum, sorted_ids);
+  count_launches(3);
+  return check_launch("moe_align_block_size_static");
+}
+
 }  // namespace moe_b200

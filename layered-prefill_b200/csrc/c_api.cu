@@ -213,6 +213,25 @@ int moe_b200_moe_align_block_size(const int32_t* topk_ids, int numel, int E, int
                                  static_cast<cudaStream_t>(stream));
 }
 
+size_t moe_b200_moe_align_static_scratch_bytes(void) { return sizeof(int) * static_cast<size_t>(static_align_scratch_ints()); }
+
+int moe_b200_moe_align_block_size_static(const int32_t* topk_ids, int numel, int E, int block_size,
+                                         int32_t* sorted_token_ids, int sorted_cap, int32_t* expert_ids,
+                                         int expert_ids_cap, int32_t* num_tokens_post_pad, void* stream) {
+  if (sorted_token_ids == nullptr || expert_ids == nullptr || num_tokens_post_pad == nullptr ||
+      (numel > 0 && topk_ids == nullptr))
+    return set_error(kStatusInvalidArgument, "moe_align_block_size_static: null pointer");
+  if (block_size > 0 && E > 0) {
+    const long long need = static_cast<long long>(numel) + static_cast<long long>(numel < E ? numel : E) * (block_size - 1);
+    if (sorted_cap < need)
+      return set_error(kStatusInvalidArgument, "moe_align_block_size_static: sorted_token_ids holds %d entries, %lld needed", sorted_cap, need);
+    if (static_cast<long long>(expert_ids_cap) * block_size < need)
+      return set_error(kStatusInvalidArgument, "moe_align_block_size_static: expert_ids holds %d entries, too few", expert_ids_cap);
+  }
+  return launch_align_block_size_static(topk_ids, numel, E, block_size, sorted_token_ids, sorted_cap, expert_ids,
+                                        expert_ids_cap, num_tokens_post_pad, static_cast<cudaStream_t>(stream));
+}
+
 int moe_b200_silu_and_mul(void* out, const void* in, int rows, int d, void* stream) {
   if (rows > 0 && (out == nullptr || in == nullptr)) return set_error(kStatusInvalidArgument, "silu_and_mul: null pointer");
   return launch_silu_and_mul(static_cast<__nv_bfloat16*>(out), static_cast<const __nv_bfloat16*>(in), rows, d,

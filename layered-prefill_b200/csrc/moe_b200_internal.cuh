@@ -42,6 +42,11 @@ int launch_align_block_size(const int* topk_ids, int numel, int E, int block_siz
                             int* expert_ids, int expert_ids_cap, int* num_post_pad, void* workspace,
                             size_t workspace_bytes, cudaStream_t stream);
 
+int static_align_scratch_ints();
+int launch_align_block_size_static(const int* topk_ids, int numel, int E, int block_size, int* sorted_ids,
+                                   int sorted_cap, int* expert_ids, int expert_ids_cap, int* num_post_pad,
+                                   cudaStream_t stream);
+
 // ---- elementwise.cu
 int launch_silu_and_mul(__nv_bfloat16* out, const __nv_bfloat16* in, int rows, int d, cudaStream_t stream);
 int launch_swigluoai_and_mul(__nv_bfloat16* out, const __nv_bfloat16* in, int rows, int d, float alpha, float limit,
