@@ -1,0 +1,118 @@
+"""Host-side logic of the tensor-parallel path with two gloo ranks on the CPU: sharding through
+FusedMoE.weight_loader, the partial sums' reduction, and the IPC handle exchange of CustomAllreduce
+(with the device calls replaced by fakes -- there is no GPU here)."""
+import os
+import socket
+import sys
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, q):
+    try:
+        sys.path.insert(0, ROOT)
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+        from layered_prefill_b200 import custom_all_reduce as car
+        from layered_prefill_b200.layer import FusedMoE
+        from oracle import moe_oracle as O
+
+        g = torch.Generator().manual_seed(0)
+        T, H, E, k, I = 10, 64, 8, 2, 64
+        x = torch.randn(T, H, generator=g).to(torch.bfloat16)
+        w13 = (torch.randn(E, 2 * I, H, generator=g) * 0.1).to(torch.bfloat16)
+        w2 = (torch.randn(E, H, I, generator=g) * 0.1).to(torch.bfloat16)
+        b13 = torch.randn(E, 2 * I, generator=g).to(torch.bfloat16)
+        b2 = torch.randn(E, H, generator=g).to(torch.bfloat16)
+        logits = torch.randn(T, E, generator=g)
+
+        layer = FusedMoE(E, k, H, I, params_dtype=torch.bfloat16, has_bias=True)
+        assert (layer.tp_size, layer.tp_rank) == (world, rank)
+        assert layer.w13_weight.shape == (E, 2 * I // world, H) and layer.w2_weight.shape == (E, H, I // world)
+        for e in range(E):
+            layer.weight_loader(layer.w13_weight, w13[e, :I], "model.layers.0.mlp.experts.0.gate_proj.weight", "w1", e)
+            layer.weight_loader(layer.w13_weight, w13[e, I:], "model.layers.0.mlp.experts.0.up_proj.weight", "w3", e)
+            layer.weight_loader(layer.w2_weight, w2[e], "model.layers.0.mlp.experts.0.down_proj.weight", "w2", e)
+            layer.weight_loader(layer.w13_bias, b13[e, :I], "experts.gate_proj.bias", "w1", e)
+            layer.weight_loader(layer.w13_bias, b13[e, I:], "experts.up_proj.bias", "w3", e)
+            layer.weight_loader(layer.w2_bias, b2[e], "experts.down_proj.bias", "w2", e)
+        sh13, sh2 = O.shard_expert_weights(w13, w2, world, rank)
+        assert torch.equal(layer.w13_weight.data, sh13) and torch.equal(layer.w2_weight.data, sh2)
+        ip = I // world
+        assert torch.equal(layer.w13_bias.data[:, :ip], b13[:, rank * ip:(rank + 1) * ip])
+        assert torch.equal(layer.w13_bias.data[:, ip:], b13[:, I + rank * ip:I + (rank + 1) * ip])
+        assert torch.equal(layer.w2_bias.data, b2 if rank == 0 else torch.zeros_like(b2))  # rank 0 only
+
+        # partial block on this rank's shard (CPU oracle), reduced over the ranks == the full block
+        tw, ti, _ = O.fused_topk(x, logits, k, True)
+        part = O.fused_experts(x, layer.w13_weight.data, layer.w2_weight.data, tw, ti, mode="exact",
+                               w13_bias=layer.w13_bias.data, w2_bias=layer.w2_bias.data).float()
+        dist.all_reduce(part)
+        full = O.fused_experts(x, w13, w2, tw, ti, mode="exact", w13_bias=b13, w2_bias=b2).float()
+        assert O.rel_l2(part, full) < 8e-3
+
+        # mapping of checkpoint names to (param, shard) as the loader uses it
+        m = FusedMoE.make_expert_params_mapping("gate_proj", "down_proj", "up_proj", num_experts=E)
+        assert len(m) == 3 * E and m[0] == ("experts.w13_", "experts.0.gate_proj.", 0, "w1")
+        assert m[1] == ("experts.w2_", "experts.0.down_proj.", 0, "w2")
+
+        # without CUDA the communicator disables itself and the all-reduce entry falls back to the process group
+        comm = car.CustomAllreduce(group=dist.new_group(backend="gloo"))
+        assert comm.disabled and comm.world_size == world
+        car._ar_comm = comm
+        t = torch.full((4, 8), float(rank + 1))
+        out = car.tensor_model_parallel_all_reduce(t)
+        assert torch.all(out == sum(range(1, world + 1)))
+        with car.capture():
+            pass
+
+        # handle exchange with fake device calls: every rank ends up with its own pointer at [rank]
+        # and the pointers "opened" from its peers' handles elsewhere
+        class FakeOps:
+            @staticmethod
+            def allocate_shared_buffer_and_handle(size):
+                return 1000 + rank, bytes([rank]) * 64
+
+            @staticmethod
+            def open_mem_handle(h):
+                return 2000 + h[0]
+        real = car.ops
+        car.ops = FakeOps
+        try:
+            ptrs = car.CustomAllreduce.create_shared_buffer(1 << 20, group=comm.gloo_group)
+        finally:
+            car.ops = real
+        assert ptrs == [1000 + r if r == rank else 2000 + r for r in range(world)]
+        assert not car.is_weak_contiguous(torch.zeros(4, 4)[:, :2]) and car.is_weak_contiguous(torch.zeros(4, 4)[2:])
+        dist.barrier()
+        dist.destroy_process_group()
+        q.put((rank, "ok"))
+    except Exception as e:  # noqa: BLE001
+        import traceback
+        q.put((rank, "".join(traceback.format_exception(e))))
+
+
+@pytest.mark.parametrize("world", [2])
+def test_tp_host_logic_two_gloo_ranks(world):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=240) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=60)
+    for rank, msg in results:
+        assert msg == "ok", f"rank {rank}: {msg}"
