@@ -8,8 +8,12 @@
 //   * tiles are 128 permuted token rows (one block of the moe_align_block_size permutation with
 //     block size 128, so a tile never mixes experts) by up to 256 weight rows;
 //   * weights stream through TMA (3-D map [K, rows, expert], 128-byte swizzle, no cluster fan-out)
-//     into a 4-stage shared-memory ring; pass 1 gathers its token rows with 16-byte cp.async into the
-//     same swizzled layout, pass 2 reads the permuted intermediate with a 2-D TMA map;
+//     into a shared-memory ring that takes all 227 KB (4 stages at N=256, 5 at N=192, 7 at N=128); the
+//     token rows (hidden states gathered through the permutation in pass 1, rows of the permuted
+//     intermediate in pass 2) come in with 16-byte cp.async from four warps, written straight into the
+//     same swizzled K-major layout, and signal the stage's barrier asynchronously
+//     (cp.async.mbarrier.arrive.noinc). Splitting the operands over the TMA unit and the LSU path
+//     measured faster than TMA for both, and padding rows cost no traffic (zero-fill);
 //   * one thread issues tcgen05.mma (M=128, N<=256, K=16 per instruction) into one of two 256-column
 //     TMEM accumulators, so the epilogue of tile i overlaps the main loop of tile i+1;
 //   * pass 1 keeps the gate rows and the matching up rows of w13 in the same tile (columns [0,BNH)
@@ -44,15 +48,14 @@ constexpr int kRingBudget = kSmemLimit - kBarrierBytes - 1024 /*alignment slack*
 constexpr int kWarpTma = 0;
 constexpr int kWarpMma = 1;
 constexpr int kWarpEpilogue0 = 2;  // 4 warps
-constexpr int kWarpGather0 = 6;    // 4 warps (gate_up pass only)
-constexpr int kThreadsGateUp = 320;
-constexpr int kThreadsDown = 192;
+constexpr int kWarpGather0 = 6;    // 4 warps: token rows by cp.async
+constexpr int kThreads = 320;
 
 struct KernelParams {
   const int* sorted_ids;
   const int* expert_ids;
   const int* num_post_pad;
-  const __nv_bfloat16* x;  // gate_up: token rows [T, K]
+  const __nv_bfloat16* x;  // token-side operand: hidden states [T, K] (gate_up) or permuted intermediate [rows, K] (down)
   int numel;
   int top_k;
   int K;
@@ -80,9 +83,8 @@ union Pack8 {
 __device__ __forceinline__ void report(int* status, int code) { atomicCAS(status, 0, code); }
 
 template <int kMode>  // 1 = gate_up, 2 = down
-__global__ void __launch_bounds__(kMode == 1 ? kThreadsGateUp : kThreadsDown, 1)
-grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                    const KernelParams p) {
+__global__ void __launch_bounds__(kThreads, 1)
+grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b, const KernelParams p) {
   extern __shared__ uint8_t smem_raw[];
   // operand stages want 1024-byte alignment in the shared window (swizzle atoms, descriptor base offset 0)
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -100,7 +102,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kMaxStages; ++s) {
-      mbar_init(&bar_full[s], kMode == 1 ? 1 + 128 : 1);
+      mbar_init(&bar_full[s], 1 + 128);
       mbar_init(&bar_empty[s], 1);
     }
     for (int a = 0; a < 2; ++a) {
@@ -109,7 +111,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     }
     fence_mbar_init();
     tma_prefetch_desc(&tmap_b);
-    if (kMode == 2) tma_prefetch_desc(&tmap_a);
   }
   if (warp == kWarpMma) {
     tmem_alloc(tmem_slot, kTmemCols);
@@ -147,8 +148,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 tma_load_3d(b_dst + p.tile_cols * 128, &tmap_b, kb * BK, p.inter + n0, e, &bar_full[s]);
               }
             } else {
-              mbar_arrive_expect_tx(&bar_full[s], static_cast<uint32_t>(kABytes) + static_cast<uint32_t>(p.mma_n) * 128u);
-              tma_load_2d(a_dst, &tmap_a, kb * BK, m_blk * BM, &bar_full[s]);
+              mbar_arrive_expect_tx(&bar_full[s], static_cast<uint32_t>(p.mma_n) * 128u);
               tma_load_3d(b_dst, &tmap_b, kb * BK, n0, e, &bar_full[s]);
             }
           } else {
@@ -310,7 +310,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       __syncwarp();
       if (lane == 0) mbar_arrive(&bar_tmem_empty[acc]);
     }
-  } else if (kMode == 1 && warp >= kWarpGather0) {
+  } else if (warp >= kWarpGather0) {
     // ------------------------------------------------------------------ token-row gather (gate_up pass)
     const int gw = warp - kWarpGather0;  // 0..3
     const int sub = lane >> 3;           // row inside a group of 4
@@ -325,7 +325,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         const int flat = p.sorted_ids[static_cast<long long>(m_blk) * BM + row0 + 16 * i];
-        src[i] = flat < p.numel ? p.x + static_cast<long long>(flat / p.top_k) * p.K + ch * 8 : nullptr;
+        if (kMode == 1)
+          src[i] = flat < p.numel ? p.x + static_cast<long long>(flat / p.top_k) * p.K + ch * 8 : nullptr;
+        else  // down pass: row p of the permuted intermediate
+          src[i] = flat < p.numel ? p.x + (static_cast<long long>(m_blk) * BM + row0 + 16 * i) * p.K + ch * 8 : nullptr;
       }
       for (int kb = 0; kb < num_kb; ++kb) {
         ok = mbar_wait(&bar_empty[s], ph ^ 1u);
@@ -487,8 +490,7 @@ int launch_grouped_gemm1(const GroupedGemmArgs& a, const __nv_bfloat16* x, const
   const int mma_n = 2 * tile_cols;
   if (int st = ensure_smem_attr<1>()) return st;
 
-  CUtensorMap map_b, map_a;
-  memset(&map_a, 0, sizeof(map_a));
+  CUtensorMap map_b;
   const uint64_t dims[3] = {static_cast<uint64_t>(a.hidden), static_cast<uint64_t>(2 * a.inter), static_cast<uint64_t>(a.num_experts)};
   const uint32_t box[3] = {BK, static_cast<uint32_t>(a.activation == 1 ? mma_n : tile_cols), 1};
   if (int st = make_map(&map_b, w13, 3, dims, box)) return st;
@@ -506,7 +508,7 @@ int launch_grouped_gemm1(const GroupedGemmArgs& a, const __nv_bfloat16* x, const
   long long tiles = static_cast<long long>(a.max_m_blocks) * p.n_tiles;
   const int grid = static_cast<int>(tiles < device_sm_count() ? tiles : device_sm_count());
   const int smem_bytes = kBarrierBytes + 1024 + p.stages * p.stage_bytes;
-  grouped_gemm_kernel<1><<<grid, kThreadsGateUp, smem_bytes, stream>>>(map_a, map_b, p);
+  grouped_gemm_kernel<1><<<grid, kThreads, smem_bytes, stream>>>(map_b, p);
   count_launches(1);
   return check_launch("grouped_gemm gate_up");
 }
@@ -520,17 +522,15 @@ int launch_grouped_gemm2(const GroupedGemmArgs& a, const __nv_bfloat16* h_sorted
   const int tile_cols = pick_down_tile(a.hidden, expected_m_blocks(a.numel, a.top_k, a.num_experts));
   if (int st = ensure_smem_attr<2>()) return st;
 
-  CUtensorMap map_a, map_b;
-  const uint64_t dims_a[2] = {static_cast<uint64_t>(a.inter), static_cast<uint64_t>(rows_cap)};
-  const uint32_t box_a[2] = {BK, BM};
-  if (int st = make_map(&map_a, h_sorted, 2, dims_a, box_a)) return st;
+  CUtensorMap map_b;
+  (void)rows_cap;
   const uint64_t dims_b[3] = {static_cast<uint64_t>(a.inter), static_cast<uint64_t>(a.hidden), static_cast<uint64_t>(a.num_experts)};
   const uint32_t box_b[3] = {BK, static_cast<uint32_t>(tile_cols), 1};
   if (int st = make_map(&map_b, w2, 3, dims_b, box_b)) return st;
 
   KernelParams p{};
   p.sorted_ids = a.sorted_ids; p.expert_ids = a.expert_ids; p.num_post_pad = a.num_post_pad;
-  p.x = nullptr; p.numel = a.numel; p.top_k = a.top_k; p.K = a.inter;
+  p.x = h_sorted; p.numel = a.numel; p.top_k = a.top_k; p.K = a.inter;
   p.n_tiles = (a.hidden + tile_cols - 1) / tile_cols; p.tile_cols = tile_cols; p.mma_n = tile_cols;
   p.out_cols = a.hidden; p.inter = a.inter; p.interleaved = 0;
   p.out = c3; p.out_ld = a.hidden; p.topk_w = topk_w; p.bias = w2_bias;
@@ -540,7 +540,7 @@ int launch_grouped_gemm2(const GroupedGemmArgs& a, const __nv_bfloat16* h_sorted
   long long tiles = static_cast<long long>(a.max_m_blocks) * p.n_tiles;
   const int grid = static_cast<int>(tiles < device_sm_count() ? tiles : device_sm_count());
   const int smem_bytes = kBarrierBytes + 1024 + p.stages * p.stage_bytes;
-  grouped_gemm_kernel<2><<<grid, kThreadsDown, smem_bytes, stream>>>(map_a, map_b, p);
+  grouped_gemm_kernel<2><<<grid, kThreads, smem_bytes, stream>>>(map_b, p);
   count_launches(1);
   return check_launch("grouped_gemm down");
 }
