@@ -34,7 +34,10 @@ if ROOT not in sys.path:
 import torch  # noqa: E402
 
 ALIASES = {"decode": "qwen3-30b-a3b-decode-t64", "prefill": "qwen3-30b-a3b-prefill-t8192",
-           "t256": "qwen3-30b-a3b-t256"}
+           "t256": "qwen3-30b-a3b-t256", "mixed": "qwen3-30b-a3b-mixed-iteration"}
+# config 4: one layered-prefill iteration of a 48-layer stack with 16 layer groups: 256 decode tokens go
+# through every layer, 8192 prefill tokens join them in the 3 layers of the designated group
+MIXED_LAYERS, MIXED_GROUP, MIXED_DECODE_T, MIXED_PREFILL_T = 48, 3, 256, 8192
 
 
 def measured_peaks():
@@ -201,9 +204,14 @@ def main():
     args = build_parser().parse_args()
     from layered_prefill_b200 import workload as W
     name = ALIASES.get(args.workload, args.workload)
-    if name not in W.WORKLOADS:
+    if name not in W.WORKLOADS and name != "qwen3-30b-a3b-mixed-iteration":
         raise SystemExit(f"unknown workload {args.workload}; known: {sorted(W.WORKLOADS)} or {sorted(ALIASES)}")
-    wl = W.WORKLOADS[name]
+    mixed = name == "qwen3-30b-a3b-mixed-iteration"
+    if mixed:
+        wl = W.with_tokens(W.WORKLOADS["qwen3-30b-a3b-prefill-t8192"], MIXED_PREFILL_T + MIXED_DECODE_T)
+        wl = W.MoeWorkload(name, wl.T, wl.H, wl.E, wl.top_k, wl.I, wl.logit_bias_std)
+    else:
+        wl = W.WORKLOADS[name]
     if args.tokens is not None:
         wl = W.with_tokens(wl, args.tokens)
 
@@ -236,8 +244,8 @@ def main():
             raise SystemExit("peer-memory all-reduce could not be initialised on this box")
 
     prefill = wl.T >= 2048
-    steps = args.steps if args.steps is not None else (200 if prefill else 2000)
-    warmup = args.warmup if args.warmup is not None else (10 if prefill else 50)
+    steps = args.steps if args.steps is not None else (20 if mixed else 200 if prefill else 2000)
+    warmup = args.warmup if args.warmup is not None else (3 if mixed else 10 if prefill else 50)
     warmup = max(warmup, 3)
     tp = world
     ip = wl.I // tp
@@ -269,10 +277,28 @@ def main():
     torch.cuda.synchronize()
     out = torch.empty_like(x)
 
-    def step(i, xin=x, lgin=logits):
+    def block(i, xin, lgin, dst):
         w13, w2 = sets[i % n_sets]
         return fused_moe.fused_moe_forward(xin, lgin, w13, w2, wl.top_k, True, "silu", inplace=False, comm=comm,
-                                           out=out)
+                                           out=dst)
+
+    if mixed:
+        # decode tokens = the last MIXED_DECODE_T rows; layers of the designated group see all rows
+        x_dec, lg_dec = x[MIXED_PREFILL_T:].contiguous(), logits[MIXED_PREFILL_T:].contiguous()
+        out_dec = torch.empty_like(x_dec)
+        group0 = MIXED_LAYERS // 2
+
+        def step(i, xin=x, lgin=logits):
+            o = None
+            for layer in range(MIXED_LAYERS):
+                if group0 <= layer < group0 + MIXED_GROUP:
+                    o = block(i * MIXED_LAYERS + layer, xin, lgin, out)
+                else:
+                    block(i * MIXED_LAYERS + layer, x_dec, lg_dec, out_dec)
+            return o
+    else:
+        def step(i, xin=x, lgin=logits):
+            return block(i, xin, lgin, out)
 
     def barrier():
         torch.cuda.synchronize()
@@ -314,6 +340,9 @@ def main():
         raise SystemExit(f"device-side wait timed out (status {status})")
 
     flops = wl.flops()
+    if mixed:
+        per_token = 2 * wl.top_k * 3 * wl.H * wl.I
+        flops = per_token * (MIXED_GROUP * wl.T + (MIXED_LAYERS - MIXED_GROUP) * MIXED_DECODE_T)
     value = flops / (ms_per_step * 1e-3) / 1e12
 
     # ---- end to end: pinned host inputs in, result out, every step
@@ -393,10 +422,61 @@ def main():
 
     # whole-block fractions of both rooflines, for the record
     blk_bytes = wl.algorithmic_bytes(n_active, tp)
-    block = {"hbm_gbs": blk_bytes / (ms_per_step * 1e-3) / 1e9,
+    block_stats = {"hbm_gbs": blk_bytes / (ms_per_step * 1e-3) / 1e9,
              "hbm_frac_of_measured": blk_bytes / (ms_per_step * 1e-3) / 1e9 / peaks["hbm_gbs"],
              "tflops_per_gpu": value / tp, "tensor_frac_of_measured_sustained": value / tp / peaks["bf16_tflops_sustained"],
              "algorithmic_bytes_per_rank": blk_bytes, "n_active_experts": n_active}
+
+    extras = {}
+    # ---- config 2's comparison: the same tokens as 16 sequential chunks of 512 (what chunked prefill does)
+    if prefill and not mixed and wl.T % 512 == 0 and wl.T >= 1024:
+        n_chunks = wl.T // 512
+        xs = [x[c * 512:(c + 1) * 512].contiguous() for c in range(n_chunks)]
+        ls = [logits[c * 512:(c + 1) * 512].contiguous() for c in range(n_chunks)]
+        oc = torch.empty_like(xs[0])
+        act_chunks = [int(torch.unique(ti[c * 512:(c + 1) * 512]).numel()) for c in range(n_chunks)]
+
+        def chunked(i):
+            for c in range(n_chunks):
+                block(i, xs[c], ls[c], oc)
+
+        for i in range(3):
+            chunked(i)
+        barrier()
+        c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = 10
+        c0.record()
+        for i in range(reps):
+            chunked(i)
+        c1.record()
+        barrier()
+        c_ms = max_over_ranks(c0.elapsed_time(c1)) / reps
+        per_expert = 3 * wl.H * ip * 2
+        extras["chunked_prefill"] = {
+            "chunks": n_chunks, "chunk_tokens": 512, "us_all_chunks": c_ms * 1e3, "us_single_pass": ms_per_step * 1e3,
+            "speedup_single_pass": c_ms / ms_per_step,
+            "weight_bytes_chunked": sum(act_chunks) * per_expert, "weight_bytes_single_pass": n_active * per_expert,
+            "expert_reload_bytes_saved": (sum(act_chunks) - n_active) * per_expert}
+    # ---- all-reduce alone (N > 1): the [T, H] bf16 reduction of this workload's batch sizes
+    if world > 1:
+        ar = {}
+        for t_ar in sorted({wl.T, MIXED_DECODE_T} if mixed else {wl.T}):
+            buf = torch.randn(t_ar, wl.H, device=dev).to(torch.bfloat16)
+            for _ in range(5):
+                comm.all_reduce(buf)
+            barrier()
+            a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            reps = 50
+            a0.record()
+            for _ in range(reps):
+                comm.all_reduce(buf)
+            a1.record()
+            barrier()
+            ar[f"T{t_ar}"] = max_over_ranks(a0.elapsed_time(a1)) / reps * 1e3
+        extras["all_reduce_us_staged"] = ar
+    if mixed:
+        extras["mixed_iteration"] = {"layers": MIXED_LAYERS, "group_layers": MIXED_GROUP, "decode_tokens": MIXED_DECODE_T,
+                                     "prefill_tokens": MIXED_PREFILL_T, "moe_path_us_per_iteration": ms_per_step * 1e3}
 
     cpu_baseline = None
     if rank == 0 and world == 1 and cpu_inputs is not None:
@@ -418,9 +498,10 @@ def main():
                        "l2": f"weights rotate over {n_sets} distinct copies ({n_sets * 3 * wl.E * wl.H * ip * 2 / 1e6:.0f} MB per rank) so no step finds them in L2",
                        "all_reduce": "fused k-slot sum + peer-memory all-reduce" if world > 1 else "none (1 GPU)"},
             "us_per_layer": ms_per_step * 1e3, "tokens_per_s": wl.T / (ms_per_step * 1e-3),
-            "roofline": roofline, "block": block, "cpu_baseline": cpu_baseline, "e2e": e2e, "gpu_launches": launches,
-            "clocks": clocks,
+            "roofline": roofline, "block": block_stats, "cpu_baseline": cpu_baseline, "e2e": e2e,
+            "gpu_launches": launches, "clocks": clocks,
         }
+        line.update(extras)
         print(json.dumps(line), flush=True)
     if world > 1:
         barrier()
