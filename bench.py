@@ -237,9 +237,21 @@ def main():
     comm = None
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=dev)
-        from layered_prefill_b200.custom_all_reduce import CustomAllreduce
-        comm = CustomAllreduce(group=dist.new_group(backend="gloo"), device=dev)
+        # NCCL announces its version on stdout while it initialises; stdout carries the one JSON line only,
+        # so file descriptor 1 points at stderr until the communicators exist.
+        sys.stdout.flush()
+        saved_stdout = os.dup(1)
+        os.dup2(2, 1)
+        try:
+            dist.init_process_group("nccl", device_id=dev)
+            from layered_prefill_b200.custom_all_reduce import CustomAllreduce
+            comm = CustomAllreduce(group=dist.new_group(backend="gloo"), device=dev)
+            dist.barrier()
+            torch.cuda.synchronize()
+        finally:
+            sys.stdout.flush()
+            os.dup2(saved_stdout, 1)
+            os.close(saved_stdout)
         if comm.disabled:
             raise SystemExit("peer-memory all-reduce could not be initialised on this box")
 

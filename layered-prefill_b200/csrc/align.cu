@@ -8,6 +8,7 @@
 // is the r-th in ascending order, where the reference's atomicAdd scatter leaves the order
 // to arrival time), and for large inputs the histogram and the scatter run on many CTAs
 // (one per 1024 flat indices) around a one-CTA scan, instead of one CTA for everything.
+#include "launch.cuh"
 #include "moe_b200_internal.cuh"
 
 namespace moe_b200 {
@@ -102,6 +103,8 @@ align_single_cta_kernel(const int* __restrict__ topk_ids, int numel, int E, int 
   __shared__ int counts[kMaxExperts];
   __shared__ int warp_totals[32];
   __shared__ int total_smem;
+  grid_dependency_launch();
+  grid_dependency_wait();
 
   for (int i = threadIdx.x; i < sorted_cap; i += kThreads) sorted_ids[i] = numel;
   for (int e = threadIdx.x; e < E; e += kThreads) counts[e] = 0;
@@ -125,6 +128,8 @@ __global__ void __launch_bounds__(kThreads)
 align_chunk_hist_kernel(const int* __restrict__ topk_ids, int numel, int E, int* __restrict__ sorted_ids,
                         int sorted_cap, int* __restrict__ chunk_hist) {
   __shared__ int counts[kMaxExperts];
+  grid_dependency_launch();
+  grid_dependency_wait();
   for (int i = blockIdx.x * kThreads + threadIdx.x; i < sorted_cap; i += gridDim.x * kThreads) sorted_ids[i] = numel;
   for (int e = threadIdx.x; e < E; e += kThreads) counts[e] = 0;
   __syncthreads();
@@ -143,6 +148,8 @@ align_scan_kernel(int num_chunks, int E, int block_size, int sorted_cap, int* __
                   int* __restrict__ cumsum) {
   __shared__ int warp_totals[32];
   __shared__ int total_smem;
+  grid_dependency_launch();
+  grid_dependency_wait();
   int run = 0;
   if (threadIdx.x < E) {
     // exclusive prefix over chunks: chunk_hist[c][e] becomes the first slot (within the expert) of
@@ -169,6 +176,8 @@ __global__ void __launch_bounds__(kThreads)
 align_chunk_scatter_kernel(const int* __restrict__ topk_ids, int numel, int E, const int* __restrict__ chunk_hist,
                            const int* __restrict__ cumsum, int* __restrict__ sorted_ids) {
   __shared__ int running[kMaxExperts];
+  grid_dependency_launch();
+  grid_dependency_wait();
   for (int e = threadIdx.x; e < E; e += kThreads)
     running[e] = cumsum[e] + chunk_hist[static_cast<size_t>(blockIdx.x) * E + e];
   __syncthreads();
@@ -189,8 +198,8 @@ int launch_align_block_size(const int* topk_ids, int numel, int E, int block_siz
   if (E <= 0 || E > kMaxExperts) return set_error(kStatusInvalidArgument, "moe_align_block_size: 1..1024 experts");
   if (block_size <= 0 || numel < 0) return set_error(kStatusInvalidArgument, "moe_align_block_size: bad sizes");
   if (numel <= kSmallNumel) {
-    align_single_cta_kernel<<<1, kThreads, 0, stream>>>(topk_ids, numel, E, block_size, sorted_ids, sorted_cap,
-                                                         expert_ids, expert_ids_cap, num_post_pad);
+    launch_pdl(align_single_cta_kernel, dim3(1), dim3(kThreads), 0, stream, topk_ids, numel, E, block_size, sorted_ids,
+               sorted_cap, expert_ids, expert_ids_cap, num_post_pad);
     count_launches(1);
     return check_launch("moe_align_block_size");
   }
@@ -200,10 +209,12 @@ int launch_align_block_size(const int* topk_ids, int numel, int E, int block_siz
   const int chunks = (numel + kThreads - 1) / kThreads;
   int* chunk_hist = static_cast<int*>(workspace);
   int* cumsum = chunk_hist + static_cast<size_t>(chunks) * E;
-  align_chunk_hist_kernel<<<chunks, kThreads, 0, stream>>>(topk_ids, numel, E, sorted_ids, sorted_cap, chunk_hist);
-  align_scan_kernel<<<1, kThreads, 0, stream>>>(chunks, E, block_size, sorted_cap, expert_ids, expert_ids_cap,
-                                                num_post_pad, chunk_hist, cumsum);
-  align_chunk_scatter_kernel<<<chunks, kThreads, 0, stream>>>(topk_ids, numel, E, chunk_hist, cumsum, sorted_ids);
+  launch_pdl(align_chunk_hist_kernel, dim3(chunks), dim3(kThreads), 0, stream, topk_ids, numel, E, sorted_ids, sorted_cap,
+             chunk_hist);
+  launch_pdl(align_scan_kernel, dim3(1), dim3(kThreads), 0, stream, chunks, E, block_size, sorted_cap, expert_ids,
+             expert_ids_cap, num_post_pad, chunk_hist, cumsum);
+  launch_pdl(align_chunk_scatter_kernel, dim3(chunks), dim3(kThreads), 0, stream, topk_ids, numel, E,
+             static_cast<const int*>(chunk_hist), static_cast<const int*>(cumsum), sorted_ids);
   count_launches(3);
   return check_launch("moe_align_block_size");
 }

@@ -25,6 +25,7 @@
 #include <vector>
 
 #include "../../include/moe_b200.h"
+#include "launch.cuh"
 #include "moe_b200_internal.cuh"
 #include "ptx.cuh"
 
@@ -180,6 +181,8 @@ template <typename T, int N>
 __global__ void __launch_bounds__(kArThreads, 1) ar_oneshot_kernel(const ArParams p) {
   __shared__ bool timed_out;
   if (threadIdx.x == 0) timed_out = false;
+  grid_dependency_launch();
+  grid_dependency_wait();
   const RankData rd = *p.rank_data;
   const uint4* ptrs[N];
 #pragma unroll
@@ -201,6 +204,8 @@ template <typename T, int N>
 __global__ void __launch_bounds__(kArThreads, 1) ar_twoshot_kernel(const ArParams p) {
   __shared__ bool timed_out;
   if (threadIdx.x == 0) timed_out = false;
+  grid_dependency_launch();
+  grid_dependency_wait();
   const RankData rd = *p.rank_data;
   const long long tid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
@@ -305,8 +310,8 @@ int launch_ar(const Comm& c, const ArParams& p, bool oneshot, cudaStream_t strea
   const int blocks = pick_blocks(p.nvec);
 #define MOE_B200_AR_CASE(n)                                                              \
   case n:                                                                                \
-    if (oneshot) ar_oneshot_kernel<T, n><<<blocks, kArThreads, 0, stream>>>(p);          \
-    else ar_twoshot_kernel<T, n><<<blocks, kArThreads, 0, stream>>>(p);                  \
+    if (oneshot) launch_pdl(ar_oneshot_kernel<T, n>, dim3(blocks), dim3(kArThreads), 0, stream, p); \
+    else launch_pdl(ar_twoshot_kernel<T, n>, dim3(blocks), dim3(kArThreads), 0, stream, p);        \
     break;
   switch (c.world) {
     MOE_B200_AR_CASE(2)

@@ -4,6 +4,7 @@
 // (moe_sum, nanovllm/layers/for_moe/moe_easy_kernel.py:26-31). All are HBM-bound: 16-byte
 // accesses, grid sized from the element count.
 #include "act_math.cuh"
+#include "launch.cuh"
 #include "moe_b200_internal.cuh"
 
 namespace moe_b200 {
@@ -58,6 +59,8 @@ __global__ void swigluoai_and_mul_kernel(__nv_bfloat16* __restrict__ out, const 
 // out[t, :] = bf16(sum_j float(in[t, j, :])), j ascending.
 __global__ void moe_sum_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out, long long T,
                                int k, int H) {
+  grid_dependency_launch();
+  grid_dependency_wait();
   const int vec_per_row = H / 8;
   const long long total = T * vec_per_row;
   for (long long v = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; v < total;
@@ -113,7 +116,8 @@ int launch_swigluoai_and_mul(__nv_bfloat16* out, const __nv_bfloat16* in, int ro
 int launch_moe_sum(const __nv_bfloat16* in, __nv_bfloat16* out, int T, int k, int H, cudaStream_t stream) {
   if (T < 0 || k <= 0 || H <= 0 || H % 8 != 0) return set_error(kStatusInvalidArgument, "moe_sum: H must be a multiple of 8");
   if (T == 0) return kStatusOk;
-  moe_sum_kernel<<<grid_for(static_cast<long long>(T) * (H / 8), 256), 256, 0, stream>>>(in, out, T, k, H);
+  launch_pdl(moe_sum_kernel, dim3(grid_for(static_cast<long long>(T) * (H / 8), 256)), dim3(256), 0, stream, in, out,
+             static_cast<long long>(T), k, H);
   count_launches(1);
   return check_launch("moe_sum");
 }

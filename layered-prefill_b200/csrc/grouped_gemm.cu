@@ -26,6 +26,7 @@
 #include <cstring>
 
 #include "act_math.cuh"
+#include "launch.cuh"
 #include "moe_b200_internal.cuh"
 #include "ptx.cuh"
 
@@ -120,6 +121,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b, const KernelPara
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  // set-up done: let the next kernel start its own, then wait for the previous kernel's results
+  grid_dependency_launch();
+  grid_dependency_wait();
 
   const int num_m_blocks = *p.num_post_pad / BM;
   const int total_tiles = num_m_blocks * p.n_tiles;
@@ -508,7 +512,9 @@ int launch_grouped_gemm1(const GroupedGemmArgs& a, const __nv_bfloat16* x, const
   long long tiles = static_cast<long long>(a.max_m_blocks) * p.n_tiles;
   const int grid = static_cast<int>(tiles < device_sm_count() ? tiles : device_sm_count());
   const int smem_bytes = kBarrierBytes + 1024 + p.stages * p.stage_bytes;
-  grouped_gemm_kernel<1><<<grid, kThreads, smem_bytes, stream>>>(map_b, p);
+  if (int st = check_cuda(launch_pdl(grouped_gemm_kernel<1>, dim3(grid), dim3(kThreads), smem_bytes, stream, map_b, p),
+                          "grouped_gemm gate_up launch"))
+    return st;
   count_launches(1);
   return check_launch("grouped_gemm gate_up");
 }
@@ -540,7 +546,9 @@ int launch_grouped_gemm2(const GroupedGemmArgs& a, const __nv_bfloat16* h_sorted
   long long tiles = static_cast<long long>(a.max_m_blocks) * p.n_tiles;
   const int grid = static_cast<int>(tiles < device_sm_count() ? tiles : device_sm_count());
   const int smem_bytes = kBarrierBytes + 1024 + p.stages * p.stage_bytes;
-  grouped_gemm_kernel<2><<<grid, kThreads, smem_bytes, stream>>>(map_b, p);
+  if (int st = check_cuda(launch_pdl(grouped_gemm_kernel<2>, dim3(grid), dim3(kThreads), smem_bytes, stream, map_b, p),
+                          "grouped_gemm down launch"))
+    return st;
   count_launches(1);
   return check_launch("grouped_gemm down");
 }

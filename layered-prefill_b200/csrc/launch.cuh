@@ -1,0 +1,46 @@
+// Kernel launch with programmatic dependent launch: the kernel may become resident before the previous
+// kernel of the stream has finished, run its set-up (barrier init, TMEM allocation, descriptor prefetch)
+// and then block in grid_dependency_wait() until that kernel's results are complete and visible.
+// Every kernel launched this way calls grid_dependency_wait() before it reads or writes anything another
+// kernel touches, so "previous kernel finished" stays transitive along the stream.
+// MOE_B200_PDL=0 in the environment switches back to plain stream-ordered launches (debugging aid).
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstdlib>
+#include <utility>
+
+namespace moe_b200 {
+
+inline bool pdl_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("MOE_B200_PDL");
+    v = (e != nullptr && e[0] == '0') ? 0 : 1;
+  }
+  return v != 0;
+}
+
+template <typename... KArgs, typename... Args>
+cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                       Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(std::forward<Args>(args))...);
+}
+
+// Blocks until the previous kernel of the stream has completed (no-op for a plain launch).
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// Lets the next kernel of the stream start becoming resident.
+__device__ __forceinline__ void grid_dependency_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+}  // namespace moe_b200

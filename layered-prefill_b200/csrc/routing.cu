@@ -12,6 +12,7 @@
 // On top of that this kernel accepts bf16 logits directly (the reference upcasts with
 // gating_output.float(), for_moe/fused_moe.py:414 -- the upcast is exact) and can fold in
 // the renormalisation topk_weights / topk_weights.sum(-1) (for_moe/fused_moe.py:417-418).
+#include "launch.cuh"
 #include "moe_b200_internal.cuh"
 
 namespace moe_b200 {
@@ -34,6 +35,8 @@ template <int E, bool kBf16In>
 __global__ void __launch_bounds__(kWarpsPerCta * 32)
 topk_softmax_pow2_kernel(const void* __restrict__ gating, float* __restrict__ topk_w, int* __restrict__ topk_ids,
                          int* __restrict__ token_expert_indices, int num_rows, int k, int renormalize) {
+  grid_dependency_launch();
+  grid_dependency_wait();
   using S = TopkShape<E>;
   constexpr int VPT = S::kVpt;
   constexpr int TPR = S::kThreadsPerRow;
@@ -241,9 +244,9 @@ void launch_pow2(const void* gating, int bf16_in, float* w, int* ids, int* tei, 
   constexpr int rows_per_cta = kWarpsPerCta * TopkShape<E>::kRowsPerWarp;
   const int blocks = (T + rows_per_cta - 1) / rows_per_cta;
   if (bf16_in)
-    topk_softmax_pow2_kernel<E, true><<<blocks, kWarpsPerCta * 32, 0, stream>>>(gating, w, ids, tei, T, k, renorm);
+    launch_pdl(topk_softmax_pow2_kernel<E, true>, dim3(blocks), dim3(kWarpsPerCta * 32), 0, stream, gating, w, ids, tei, T, k, renorm);
   else
-    topk_softmax_pow2_kernel<E, false><<<blocks, kWarpsPerCta * 32, 0, stream>>>(gating, w, ids, tei, T, k, renorm);
+    launch_pdl(topk_softmax_pow2_kernel<E, false>, dim3(blocks), dim3(kWarpsPerCta * 32), 0, stream, gating, w, ids, tei, T, k, renorm);
 }
 
 }  // namespace
