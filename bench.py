@@ -140,6 +140,8 @@ def build_parser():
     ap.add_argument("--tokens", type=int, default=None, help="override the workload's token count (profiling)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--only-steps", action="store_true",
+                    help="stop after the timed steps (no e2e, roofline or comparison legs): for ncu launch lists")
     return ap
 
 
@@ -356,6 +358,18 @@ def main():
         per_token = 2 * wl.top_k * 3 * wl.H * wl.I
         flops = per_token * (MIXED_GROUP * wl.T + (MIXED_LAYERS - MIXED_GROUP) * MIXED_DECODE_T)
     value = flops / (ms_per_step * 1e-3) / 1e12
+
+    if args.only_steps:
+        sampler.stop()
+        if rank == 0:
+            print(json.dumps({"metric": "moe_block_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world,
+                              "steps": steps, "warmup": warmup, "ms_per_step": ms_per_step,
+                              "config": {"workload": wl.name}, "gpu_launches": launches, "only_steps": True}), flush=True)
+        if world > 1:
+            barrier()
+            comm.close()
+            dist.destroy_process_group()
+        return
 
     # ---- end to end: pinned host inputs in, result out, every step
     e2e = None
