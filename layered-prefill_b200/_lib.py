@@ -10,7 +10,8 @@ import os
 from ctypes import POINTER, c_char_p, c_float, c_int, c_int32, c_int64, c_size_t, c_uint8, c_void_p
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libmoe_b200.so")
+# MOE_B200_LIB points at another build of the same library (A/B comparisons of kernel variants)
+LIB_PATH = os.environ.get("MOE_B200_LIB") or os.path.join(_HERE, "libmoe_b200.so")
 
 STATUS_NAMES = {
     0: "OK", 1: "INVALID_ARGUMENT", 2: "CUDA_ERROR", 3: "WORKSPACE_TOO_SMALL", 4: "DEVICE_TIMEOUT",

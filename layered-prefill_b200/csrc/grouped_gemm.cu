@@ -243,11 +243,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b, const KernelPara
           __nv_bfloat16* out_row = p.out + pos * p.out_ld;
           if (!p.interleaved) {
             const __nv_bfloat16* bias_g = p.bias ? p.bias + static_cast<long long>(e) * 2 * p.inter : nullptr;
-            for (int c = 0; c < p.tile_cols; c += 16) {
-              uint32_t g[16], u[16];
-              tmem_ld_x16(taddr + c, g);
-              tmem_ld_x16(taddr + p.tile_cols + c, u);
-              tmem_ld_wait();
+            // Two 16-column chunks in flight: the TMEM loads of the next chunk overlap the math of this one.
+            uint32_t g0[16], u0[16], g1[16], u1[16];
+            auto finish = [&](const uint32_t (&g)[16], const uint32_t (&u)[16], int c) {
               const int col = n0 + c;
               if (valid && col < p.out_cols) {
                 Pack8 o[2];
@@ -259,11 +257,27 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b, const KernelPara
                     gf += __bfloat162float(bias_g[col + j]);
                     uf += __bfloat162float(bias_g[p.inter + col + j]);
                   }
-                  o[j >> 3].h[j & 7] = silu_mul_bf16(__float2bfloat16_rn(gf), __float2bfloat16_rn(uf));
+                  o[j >> 3].h[j & 7] = silu_mul_bf16_fast(__float2bfloat16_rn(gf), __float2bfloat16_rn(uf));
                 }
                 *reinterpret_cast<uint4*>(out_row + col) = o[0].u;
                 *reinterpret_cast<uint4*>(out_row + col + 8) = o[1].u;
               }
+            };
+            tmem_ld_x16(taddr, g0);
+            tmem_ld_x16(taddr + p.tile_cols, u0);
+            for (int c = 0; c < p.tile_cols; c += 32) {
+              tmem_ld_wait();
+              if (c + 16 < p.tile_cols) {
+                tmem_ld_x16(taddr + c + 16, g1);
+                tmem_ld_x16(taddr + p.tile_cols + c + 16, u1);
+              }
+              finish(g0, u0, c);
+              tmem_ld_wait();
+              if (c + 32 < p.tile_cols) {
+                tmem_ld_x16(taddr + c + 32, g0);
+                tmem_ld_x16(taddr + p.tile_cols + c + 32, u0);
+              }
+              if (c + 16 < p.tile_cols) finish(g1, u1, c + 16);
             }
           } else {
             const __nv_bfloat16* bias_g = p.bias ? p.bias + static_cast<long long>(e) * 2 * p.inter : nullptr;

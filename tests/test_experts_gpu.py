@@ -151,3 +151,36 @@ def test_prefill_config_properties_at_full_size():
     want = O.moe_block(inp["x"][idx], inp["router_logits"][idx], inp["w13"], inp["w2"], wl.top_k, True)
     got = out.cpu()[idx]
     assert O.rel_l2(got, want) <= REL_L2 and O.max_abs(got, want) <= MAX_ABS
+
+
+def test_block_can_be_replayed_from_a_cuda_graph():
+    """The reference replays its decode layers from CUDA graphs (models/qwen3_moe.py:648-763): the whole block
+    must be capturable -- no host synchronisation, no allocation once the workspace exists -- and a replay on
+    new inputs in the same buffers must give the new result."""
+    from layered_prefill_b200 import fused_moe
+    g = torch.Generator().manual_seed(21)
+    T, H, E, k, I = 64, 512, 32, 4, 128
+    d = _dev()
+    w13 = (torch.randn(E, 2 * I, H, generator=g) * 0.05).to(torch.bfloat16)
+    w2 = (torch.randn(E, H, I, generator=g) * 0.05).to(torch.bfloat16)
+    xs = [torch.randn(T, H, generator=g).to(torch.bfloat16) for _ in range(2)]
+    lgs = [torch.randn(T, E, generator=g).to(torch.bfloat16) for _ in range(2)]
+    x_buf, lg_buf, out = xs[0].to(d), lgs[0].to(d), torch.empty(T, H, dtype=torch.bfloat16, device=d)
+    w13d, w2d = w13.to(d), w2.to(d)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(2):  # warm-up: sizes the workspace
+            fused_moe.fused_moe_forward(x_buf, lg_buf, w13d, w2d, k, True, inplace=False, out=out)
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        fused_moe.fused_moe_forward(x_buf, lg_buf, w13d, w2d, k, True, inplace=False, out=out)
+    for i in (1, 0, 1):
+        x_buf.copy_(xs[i])
+        lg_buf.copy_(lgs[i])
+        graph.replay()
+        torch.cuda.synchronize()
+        want = O.moe_block(xs[i], lgs[i], w13, w2, k, True)
+        assert O.rel_l2(out.cpu(), want) <= REL_L2 and O.max_abs(out.cpu(), want) <= MAX_ABS
+    _check_status()
