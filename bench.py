@@ -139,6 +139,9 @@ def build_parser():
     ap.add_argument("--weight-sets", type=int, default=4, help="distinct weight copies rotated through (L2 defeat)")
     ap.add_argument("--tokens", type=int, default=None, help="override the workload's token count (profiling)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-graph", action="store_true",
+                    help="launch every step eagerly (default: decode-sized steps replay a captured CUDA graph, as the "
+                         "reference does for batches up to 1024 tokens)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--only-steps", action="store_true",
                     help="stop after the timed steps (no e2e, roofline or comparison legs): for ncu launch lists")
@@ -332,6 +335,33 @@ def main():
     for i in range(warmup):
         step(i)
     barrier()
+    # ---- decode-sized batches: one captured graph per weight set (the reference replays its decode layers
+    # from CUDA graphs up to 1024 tokens, nanovllm/models/qwen3_moe.py:648-763); larger batches stay eager
+    use_graph = (not args.no_graph) and (not mixed) and wl.T <= 1024
+    launches_per_graph = 0
+    if use_graph:
+        graphs = []
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for s_idx in range(n_sets):
+                l0 = lib.moe_b200_launch_count()
+                gph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(gph, stream=side):
+                    block(s_idx, x, logits, out)
+                launches_per_graph = int(lib.moe_b200_launch_count() - l0)
+                graphs.append(gph)
+        torch.cuda.current_stream().wait_stream(side)
+        eager_step = step
+
+        def step(i, xin=x, lgin=logits):  # noqa: F811
+            if xin is x and lgin is logits:
+                graphs[i % n_sets].replay()
+                return out
+            return eager_step(i, xin, lgin)
+        for i in range(max(3, n_sets)):
+            step(i)
+        barrier()
     if ops.read_status(dev) != 0:
         raise SystemExit("device-side wait timed out during warm-up")
 
@@ -346,6 +376,8 @@ def main():
     barrier()
     t_wall1 = time.perf_counter()
     launches = int(lib.moe_b200_launch_count() - launches0)
+    if use_graph:
+        launches = launches_per_graph * steps  # replayed kernels are not seen by the library's launch counter
     ms_total = max_over_ranks(ev0.elapsed_time(ev1))
     ms_per_step = ms_total / steps
     clocks = sampler.summary(t_wall0, t_wall1)
@@ -554,6 +586,7 @@ def main():
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": wl.name, "T": wl.T, "H": wl.H, "E": wl.E, "top_k": wl.top_k, "I": wl.I,
                        "tensor_parallel": tp, "I_per_rank": ip,
+                       "launch": "cuda graph replay per step" if use_graph else "eager launches",
                        "l2": f"weights rotate over {n_sets} distinct copies ({n_sets * 3 * wl.E * wl.H * ip * 2 / 1e6:.0f} MB per rank) so no step finds them in L2",
                        "all_reduce": "fused k-slot sum + peer-memory all-reduce" if world > 1 else "none (1 GPU)"},
             "us_per_layer": ms_per_step * 1e3, "tokens_per_s": wl.T / (ms_per_step * 1e-3),

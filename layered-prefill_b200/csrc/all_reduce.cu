@@ -328,20 +328,23 @@ int launch_ar(const Comm& c, const ArParams& p, bool oneshot, cudaStream_t strea
 
 // Resolves the device tuple of peer pointers for `input` (registered, or being captured into a graph).
 int resolve_rank_data(Comm& c, const void* input, cudaStream_t stream, RankData** out) {
+  // a buffer registered up front (the staging buffer) is usable as is, inside a capture too
+  auto it = c.buffers.find(input);
+  if (it != c.buffers.end()) {
+    *out = it->second;
+    return kStatusOk;
+  }
   cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
   if (int st = check_cuda(cudaStreamIsCapturing(stream, &cap), "cudaStreamIsCapturing")) return st;
   if (cap == cudaStreamCaptureStatusActive) {
+    // an address met during graph capture: its peers' addresses are filled in by register_graph_buffers
     if (c.rank_data_next + c.graph_unreg.size() + 1 > c.rank_data_end)
       return set_error(kStatusTooLarge, "all_reduce: rank data buffer is full");
     *out = c.rank_data_next + c.graph_unreg.size();
     c.graph_unreg.push_back(const_cast<void*>(input));
     return kStatusOk;
   }
-  auto it = c.buffers.find(input);
-  if (it == c.buffers.end())
-    return set_error(kStatusNotRegistered, "buffer address %llu is not registered!", static_cast<unsigned long long>(reinterpret_cast<uintptr_t>(input)));
-  *out = it->second;
-  return kStatusOk;
+  return set_error(kStatusNotRegistered, "buffer address %llu is not registered!", static_cast<unsigned long long>(reinterpret_cast<uintptr_t>(input)));
 }
 
 Comm* as_comm(int64_t h) { return reinterpret_cast<Comm*>(static_cast<intptr_t>(h)); }
