@@ -115,14 +115,15 @@ topk_softmax_pow2_kernel(const void* __restrict__ gating, float* __restrict__ to
         }
       }
     }
-#pragma unroll
-    for (int mask = TPR / 2; mask > 0; mask /= 2) {
-      const float other = __shfl_xor_sync(0xffffffffu, best, mask, TPR);
-      const int other_expert = __shfl_xor_sync(0xffffffffu, expert, mask, TPR);
-      if (other > best || (other == best && other_expert < expert)) {
-        best = other;
-        expert = other_expert;
-      }
+    // Consensus over the row's lanes: the largest value and, among the lanes that hold it, the smallest
+    // expert index -- what the reference's compare-and-swap butterfly arrives at, in two warp reductions.
+    // Values are softmax probabilities (>= 0) or the -10000 blanking mark, so their bit patterns order
+    // like signed integers.
+    if constexpr (TPR > 1) {
+      const unsigned row_lanes = TPR == 32 ? 0xffffffffu : (((1u << TPR) - 1u) << ((lane / TPR) * TPR));
+      const int top = __reduce_max_sync(row_lanes, __float_as_int(best));
+      expert = __reduce_min_sync(row_lanes, __float_as_int(best) == top ? expert : 0x7fffffff);
+      best = __int_as_float(top);
     }
     if (g == k_idx % TPR) {
       const int slot = k_idx / TPR;
