@@ -102,6 +102,30 @@ def main():
     red = layer.maybe_all_reduce_tensor_model_parallel(part)
     assert torch.equal(red, out)
 
+    # ---- 4. CUDA-graph capture of the all-reduce on an unregistered tensor: the address met during capture
+    # is registered with the peers when the capture() context ends (custom_all_reduce.py:206-239)
+    inp = torch.full((128, 1024), float(rank + 1), dtype=torch.bfloat16, device=dev)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        with car.capture():
+            warm = car.tensor_model_parallel_all_reduce(inp)  # warm-up outside capture: allocation pattern only
+            assert warm.shape == inp.shape
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                res = car.tensor_model_parallel_all_reduce(inp)
+    torch.cuda.current_stream().wait_stream(side)
+    dist.barrier()
+    for rep in range(3):
+        inp.fill_(float(rank + 1 + rep))
+        torch.cuda.synchronize()
+        dist.barrier()
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.all(res == sum(r + 1 + rep for r in range(world))), f"graph replay {rep}"
+        dist.barrier()
+    assert ops.read_status(dev) == 0
+
     dist.barrier()
     comm.close()
     dist.destroy_process_group()
