@@ -83,6 +83,97 @@ union Pack8 {
 
 __device__ __forceinline__ void report(int* status, int code) { atomicCAS(status, 0, code); }
 
+// Epilogue of one 128-row tile for the 32 rows one warp may read from TMEM (taddr = its lane quarter and
+// the accumulator's first column). pos = permuted row, flat = t*k+j of that row (>= numel on padding rows).
+template <int kMode>
+__device__ __forceinline__ void epilogue_rows(const KernelParams& p, uint32_t taddr, long long pos, int flat,
+                                              bool valid, float w, int e, int n0) {
+  if (kMode == 1) {
+    __nv_bfloat16* out_row = p.out + pos * p.out_ld;
+    if (!p.interleaved) {
+      const __nv_bfloat16* bias_g = p.bias ? p.bias + static_cast<long long>(e) * 2 * p.inter : nullptr;
+      // Two 16-column chunks in flight: the TMEM loads of the next chunk overlap the math of this one.
+      uint32_t g0[16], u0[16], g1[16], u1[16];
+      auto finish = [&](const uint32_t (&g)[16], const uint32_t (&u)[16], int c) {
+        const int col = n0 + c;
+        if (valid && col < p.out_cols) {
+          Pack8 o[2];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            float gf = __uint_as_float(g[j]);
+            float uf = __uint_as_float(u[j]);
+            if (bias_g) {
+              gf += __bfloat162float(bias_g[col + j]);
+              uf += __bfloat162float(bias_g[p.inter + col + j]);
+            }
+            o[j >> 3].h[j & 7] = silu_mul_bf16_fast(__float2bfloat16_rn(gf), __float2bfloat16_rn(uf));
+          }
+          *reinterpret_cast<uint4*>(out_row + col) = o[0].u;
+          *reinterpret_cast<uint4*>(out_row + col + 8) = o[1].u;
+        }
+      };
+      tmem_ld_x16(taddr, g0);
+      tmem_ld_x16(taddr + p.tile_cols, u0);
+      for (int c = 0; c < p.tile_cols; c += 32) {
+        tmem_ld_wait();
+        if (c + 16 < p.tile_cols) {
+          tmem_ld_x16(taddr + c + 16, g1);
+          tmem_ld_x16(taddr + p.tile_cols + c + 16, u1);
+        }
+        finish(g0, u0, c);
+        tmem_ld_wait();
+        if (c + 32 < p.tile_cols) {
+          tmem_ld_x16(taddr + c + 32, g0);
+          tmem_ld_x16(taddr + p.tile_cols + c + 32, u0);
+        }
+        if (c + 16 < p.tile_cols) finish(g1, u1, c + 16);
+      }
+    } else {
+      const __nv_bfloat16* bias_g = p.bias ? p.bias + static_cast<long long>(e) * 2 * p.inter : nullptr;
+      for (int c = 0; c < p.tile_cols; c += 8) {
+        uint32_t gu[16];
+        tmem_ld_x16(taddr + 2 * c, gu);
+        tmem_ld_wait();
+        const int col = n0 + c;
+        if (valid && col < p.out_cols) {
+          Pack8 o;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            float gf = __uint_as_float(gu[2 * j]);
+            float uf = __uint_as_float(gu[2 * j + 1]);
+            if (bias_g) {
+              gf += __bfloat162float(bias_g[2 * (col + j)]);
+              uf += __bfloat162float(bias_g[2 * (col + j) + 1]);
+            }
+            o.h[j] = swigluoai_bf16(__float2bfloat16_rn(gf), __float2bfloat16_rn(uf), p.alpha, p.limit);
+          }
+          *reinterpret_cast<uint4*>(out_row + col) = o.u;
+        }
+      }
+    }
+  } else {
+    __nv_bfloat16* out_row = p.out + static_cast<long long>(valid ? flat : 0) * p.out_ld;
+    const __nv_bfloat16* bias_d = p.bias ? p.bias + static_cast<long long>(e) * p.out_cols : nullptr;
+    for (int c = 0; c < p.tile_cols; c += 16) {
+      uint32_t d[16];
+      tmem_ld_x16(taddr + c, d);
+      tmem_ld_wait();
+      const int col = n0 + c;
+      if (valid && col < p.out_cols) {
+        Pack8 o[2];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          float v = __uint_as_float(d[j]);
+          if (bias_d) v += __bfloat162float(bias_d[col + j]);
+          o[j >> 3].h[j & 7] = __float2bfloat16_rn(v * w);
+        }
+        *reinterpret_cast<uint4*>(out_row + col) = o[0].u;
+        *reinterpret_cast<uint4*>(out_row + col + 8) = o[1].u;
+      }
+    }
+  }
+}
+
 template <int kMode>  // 1 = gate_up, 2 = down
 __global__ void __launch_bounds__(kThreads, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b, const KernelParams p) {
@@ -131,87 +222,95 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b, const KernelPara
 
   if (warp == kWarpTma) {
     // ------------------------------------------------------------------ TMA producer
-    uint32_t s = 0, ph = 0;
-    bool ok = true;
-    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-      const int m_blk = tile / p.n_tiles;
-      const int n0 = (tile % p.n_tiles) * p.tile_cols;
-      const int e = p.expert_ids[m_blk];
-      for (int kb = 0; kb < num_kb; ++kb) {
-        if (lane == 0) {
-          ok = mbar_wait(&bar_empty[s], ph ^ 1u);
-          if (ok) {
-            uint8_t* a_dst = ring + s * stage_bytes;
-            uint8_t* b_dst = a_dst + kABytes;
-            if (kMode == 1) {
-              mbar_arrive_expect_tx(&bar_full[s], static_cast<uint32_t>(p.mma_n) * 128u);
-              if (p.interleaved) {
-                tma_load_3d(b_dst, &tmap_b, kb * BK, 2 * n0, e, &bar_full[s]);
-              } else {
-                tma_load_3d(b_dst, &tmap_b, kb * BK, n0, e, &bar_full[s]);
-                tma_load_3d(b_dst + p.tile_cols * 128, &tmap_b, kb * BK, p.inter + n0, e, &bar_full[s]);
-              }
-            } else {
-              mbar_arrive_expect_tx(&bar_full[s], static_cast<uint32_t>(p.mma_n) * 128u);
-              tma_load_3d(b_dst, &tmap_b, kb * BK, n0, e, &bar_full[s]);
-            }
-          } else {
+    if (lane == 0) {
+      uint32_t s = 0, ph = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        const int m_blk = tile / p.n_tiles;
+        const int n0 = (tile % p.n_tiles) * p.tile_cols;
+        const int e = p.expert_ids[m_blk];
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&bar_empty[s], ph ^ 1u)) {
             report(p.status, kErrWaitEmpty);
+            ok = false;
+            break;
           }
-        }
-        ok = __shfl_sync(0xffffffffu, ok, 0);
-        if (!ok) break;
-        if (++s == num_stages) {
-          s = 0;
-          ph ^= 1u;
+          uint8_t* b_dst = ring + s * stage_bytes + kABytes;
+          mbar_arrive_expect_tx(&bar_full[s], static_cast<uint32_t>(p.mma_n) * 128u);
+          if (kMode == 1 && !p.interleaved) {
+            tma_load_3d(b_dst, &tmap_b, kb * BK, n0, e, &bar_full[s]);
+            tma_load_3d(b_dst + p.tile_cols * 128, &tmap_b, kb * BK, p.inter + n0, e, &bar_full[s]);
+          } else {
+            tma_load_3d(b_dst, &tmap_b, kb * BK, kMode == 1 ? 2 * n0 : n0, e, &bar_full[s]);
+          }
+          if (++s == num_stages) {
+            s = 0;
+            ph ^= 1u;
+          }
         }
       }
     }
+    __syncwarp();
   } else if (warp == kWarpMma) {
     // ------------------------------------------------------------------ MMA issuer
-    const uint32_t idesc = umma_idesc_bf16(BM, static_cast<uint32_t>(p.mma_n));
-    uint32_t s = 0, ph = 0;
-    uint32_t tile_iter = 0;
-    bool ok = true;
-    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tile_iter) {
-      const uint32_t acc = tile_iter & 1u;
-      const uint32_t acc_ph = (tile_iter >> 1) & 1u;
-      if (lane == 0) {
-        ok = mbar_wait(&bar_tmem_empty[acc], acc_ph ^ 1u);
-        if (!ok) report(p.status, kErrWaitTmemEmpty);
-      }
-      ok = __shfl_sync(0xffffffffu, ok, 0);
-      if (!ok) break;
-      tc_fence_after_sync();
-      const uint32_t d_tmem = tmem_base + acc * kAccCols;
-      for (int kb = 0; kb < num_kb; ++kb) {
-        if (lane == 0) {
-          ok = mbar_wait(&bar_full[s], ph);
-          if (ok) {
-            tc_fence_after_sync();
-            const uint32_t a_addr = smem_u32(ring + s * stage_bytes);
-            const uint64_t adesc = umma_desc_k_sw128(a_addr);
-            const uint64_t bdesc = umma_desc_k_sw128(a_addr + kABytes);
-#pragma unroll
-            for (int k = 0; k < BK / kUmmaK; ++k) {
-              // advancing 16 bf16 = 32 bytes along K inside the swizzled row: +2 in 16-byte units
-              umma_bf16(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
-            }
-            umma_commit(&bar_empty[s]);
-          } else {
+    // One thread runs the whole loop. The tensor pipe queues next to nothing: a gap of ~100 cycles between
+    // two tcgen05.mma of this thread is a bubble (measured: four dependent shared-memory accesses per K
+    // block cost 22 % of the MMA rate). So the barrier needed next is probed while MMAs just issued still
+    // execute, and the loop only blocks when the probe failed.
+    if (lane == 0) {
+      const uint32_t idesc = umma_idesc_bf16(BM, static_cast<uint32_t>(p.mma_n));
+      const uint64_t adesc0 = umma_desc_k_sw128(smem_u32(ring));
+      const uint64_t bdesc0 = umma_desc_k_sw128(smem_u32(ring) + kABytes);
+      const uint64_t stage_step = stage_bytes >> 4;  // descriptors address shared memory in 16-byte units
+      const int my_tiles = static_cast<int>(blockIdx.x) < total_tiles
+                               ? (total_tiles - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x)
+                               : 0;
+      uint32_t s = 0, ph = 0;
+      uint64_t stage_off = 0;
+      bool ok = true;
+      bool acc_ready = false, stage_ready = false;
+      for (int t = 0; t < my_tiles && ok; ++t) {
+        const uint32_t acc = static_cast<uint32_t>(t) & 1u;
+        const uint32_t acc_ph = (static_cast<uint32_t>(t) >> 1) & 1u;
+        if (!acc_ready && !mbar_wait(&bar_tmem_empty[acc], acc_ph ^ 1u)) {
+          report(p.status, kErrWaitTmemEmpty);
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * kAccCols;
+        uint32_t accumulate = 0;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!stage_ready && !mbar_wait(&bar_full[s], ph)) {
             report(p.status, kErrWaitFull);
+            ok = false;
+            break;
           }
+          const uint64_t adesc = adesc0 + stage_off;
+          const uint64_t bdesc = bdesc0 + stage_off;
+          // advancing 16 bf16 = 32 bytes along K inside the swizzled row: +2 in 16-byte units
+          umma_bf16(d_tmem, adesc, bdesc, idesc, accumulate);
+          umma_bf16(d_tmem, adesc + 2, bdesc + 2, idesc, 1u);
+          uint32_t s_next = s + 1, ph_next = ph;
+          if (s_next == num_stages) {
+            s_next = 0;
+            ph_next ^= 1u;
+          }
+          const bool last_kb = kb + 1 == num_kb;
+          if (!last_kb || t + 1 < my_tiles) stage_ready = mbar_try_wait(&bar_full[s_next], ph_next);
+          if (last_kb && t + 1 < my_tiles)
+            acc_ready = mbar_try_wait(&bar_tmem_empty[acc ^ 1u], ((static_cast<uint32_t>(t + 1) >> 1) & 1u) ^ 1u);
+          umma_bf16(d_tmem, adesc + 4, bdesc + 4, idesc, 1u);
+          umma_bf16(d_tmem, adesc + 6, bdesc + 6, idesc, 1u);
+          accumulate = 1u;
+          umma_commit(&bar_empty[s]);
+          stage_off = s_next == 0 ? 0 : stage_off + stage_step;
+          s = s_next;
+          ph = ph_next;
         }
-        ok = __shfl_sync(0xffffffffu, ok, 0);
-        if (!ok) break;
-        if (++s == num_stages) {
-          s = 0;
-          ph ^= 1u;
-        }
+        if (ok) umma_commit(&bar_tmem_full[acc]);
       }
-      if (ok && lane == 0) umma_commit(&bar_tmem_full[acc]);
-      __syncwarp();
     }
+    __syncwarp();
   } else if (warp >= kWarpEpilogue0 && warp < kWarpEpilogue0 + 4) {
     // ------------------------------------------------------------------ epilogue
     const int q = warp & 3;  // TMEM lane quarter this warp may read
@@ -239,90 +338,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b, const KernelPara
 
       if (__any_sync(0xffffffffu, valid)) {
         const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * kAccCols;
-        if (kMode == 1) {
-          __nv_bfloat16* out_row = p.out + pos * p.out_ld;
-          if (!p.interleaved) {
-            const __nv_bfloat16* bias_g = p.bias ? p.bias + static_cast<long long>(e) * 2 * p.inter : nullptr;
-            // Two 16-column chunks in flight: the TMEM loads of the next chunk overlap the math of this one.
-            uint32_t g0[16], u0[16], g1[16], u1[16];
-            auto finish = [&](const uint32_t (&g)[16], const uint32_t (&u)[16], int c) {
-              const int col = n0 + c;
-              if (valid && col < p.out_cols) {
-                Pack8 o[2];
-#pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                  float gf = __uint_as_float(g[j]);
-                  float uf = __uint_as_float(u[j]);
-                  if (bias_g) {
-                    gf += __bfloat162float(bias_g[col + j]);
-                    uf += __bfloat162float(bias_g[p.inter + col + j]);
-                  }
-                  o[j >> 3].h[j & 7] = silu_mul_bf16_fast(__float2bfloat16_rn(gf), __float2bfloat16_rn(uf));
-                }
-                *reinterpret_cast<uint4*>(out_row + col) = o[0].u;
-                *reinterpret_cast<uint4*>(out_row + col + 8) = o[1].u;
-              }
-            };
-            tmem_ld_x16(taddr, g0);
-            tmem_ld_x16(taddr + p.tile_cols, u0);
-            for (int c = 0; c < p.tile_cols; c += 32) {
-              tmem_ld_wait();
-              if (c + 16 < p.tile_cols) {
-                tmem_ld_x16(taddr + c + 16, g1);
-                tmem_ld_x16(taddr + p.tile_cols + c + 16, u1);
-              }
-              finish(g0, u0, c);
-              tmem_ld_wait();
-              if (c + 32 < p.tile_cols) {
-                tmem_ld_x16(taddr + c + 32, g0);
-                tmem_ld_x16(taddr + p.tile_cols + c + 32, u0);
-              }
-              if (c + 16 < p.tile_cols) finish(g1, u1, c + 16);
-            }
-          } else {
-            const __nv_bfloat16* bias_g = p.bias ? p.bias + static_cast<long long>(e) * 2 * p.inter : nullptr;
-            for (int c = 0; c < p.tile_cols; c += 8) {
-              uint32_t gu[16];
-              tmem_ld_x16(taddr + 2 * c, gu);
-              tmem_ld_wait();
-              const int col = n0 + c;
-              if (valid && col < p.out_cols) {
-                Pack8 o;
-#pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                  float gf = __uint_as_float(gu[2 * j]);
-                  float uf = __uint_as_float(gu[2 * j + 1]);
-                  if (bias_g) {
-                    gf += __bfloat162float(bias_g[2 * (col + j)]);
-                    uf += __bfloat162float(bias_g[2 * (col + j) + 1]);
-                  }
-                  o.h[j] = swigluoai_bf16(__float2bfloat16_rn(gf), __float2bfloat16_rn(uf), p.alpha, p.limit);
-                }
-                *reinterpret_cast<uint4*>(out_row + col) = o.u;
-              }
-            }
-          }
-        } else {
-          __nv_bfloat16* out_row = p.out + static_cast<long long>(valid ? flat : 0) * p.out_ld;
-          const __nv_bfloat16* bias_d = p.bias ? p.bias + static_cast<long long>(e) * p.out_cols : nullptr;
-          for (int c = 0; c < p.tile_cols; c += 16) {
-            uint32_t d[16];
-            tmem_ld_x16(taddr + c, d);
-            tmem_ld_wait();
-            const int col = n0 + c;
-            if (valid && col < p.out_cols) {
-              Pack8 o[2];
-#pragma unroll
-              for (int j = 0; j < 16; ++j) {
-                float v = __uint_as_float(d[j]);
-                if (bias_d) v += __bfloat162float(bias_d[col + j]);
-                o[j >> 3].h[j & 7] = __float2bfloat16_rn(v * w);
-              }
-              *reinterpret_cast<uint4*>(out_row + col) = o[0].u;
-              *reinterpret_cast<uint4*>(out_row + col + 8) = o[1].u;
-            }
-          }
-        }
+        epilogue_rows<kMode>(p, taddr, pos, flat, valid, w, e, n0);
       }
       tc_fence_before_sync();
       __syncwarp();

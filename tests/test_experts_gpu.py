@@ -62,6 +62,36 @@ def test_fused_experts_small_shapes(T, H, E, k, I):
     _run_case(T, H, E, k, I, seed=T + H)
 
 
+@pytest.mark.parametrize("T,H,E,k,I,kw", [
+    (1024, 256, 8, 2, 128, {}),                       # 256 rows per expert on average: several blocks each
+    (900, 320, 4, 2, 192, {"skew": 2.0}),             # 96-column gate_up tiles, H = 256 + 64 (ragged last down tile)
+    (1024, 512, 16, 4, 96, {"skew": 3.0}),            # K tail in the down pass, busy and idle experts
+    (1000, 256, 4, 2, 64, {"activation": "swigluoai", "bias": True, "scale": 0.1}),  # interleaved gate/up rows
+    (700, 128, 2, 1, 48, {"bias": True}),             # 48-column tiles, top-1
+])
+def test_fused_experts_many_blocks_per_expert(T, H, E, k, I, kw):
+    """Prefill-like ratios (hundreds of rows per expert) at sizes the oracle still finishes quickly."""
+    _run_case(T, H, E, k, I, seed=T + I, **kw)
+
+
+def test_odd_block_counts_and_empty_experts():
+    from layered_prefill_b200 import fused_moe
+    g = torch.Generator().manual_seed(21)
+    T, H, E, I = 800, 256, 8, 128
+    x = torch.randn(T, H, generator=g).to(torch.bfloat16)
+    w13 = (torch.randn(E, 2 * I, H, generator=g) * 0.05).to(torch.bfloat16)
+    w2 = (torch.randn(E, H, I, generator=g) * 0.05).to(torch.bfloat16)
+    # expert 2: 800 rows (7 blocks), expert 5: 500 rows, expert 7: 300 rows (3 blocks), the others none
+    second = torch.where(torch.arange(T) < 500, 5, 7)
+    ti = torch.stack([torch.full((T,), 2), second], dim=1).to(torch.int32)
+    tw = torch.rand(T, 2, generator=g)
+    want = O.fused_experts(x, w13, w2, tw, ti)
+    d = _dev()
+    got = fused_moe.fused_experts(x.to(d), w13.to(d), w2.to(d), None, None, tw.to(d), ti.to(d)).cpu()
+    _check_status()
+    assert O.rel_l2(got, want) <= REL_L2 and O.max_abs(got, want) <= MAX_ABS
+
+
 def test_fused_experts_with_biases_and_swigluoai():
     _run_case(40, 256, 8, 2, 64, seed=3, bias=True)
     _run_case(40, 256, 8, 2, 64, seed=4, activation="swigluoai", bias=True, scale=0.1)
