@@ -125,6 +125,27 @@ int moe_b200_fused_experts(const void* x, const void* w13, const void* w2, const
                            int32_t* status_word, void* stream);
 
 /*
+ * fp8 (e4m3, w8a8) variant of fused_experts with 128 x 128 block-scaled weights and activations quantised
+ * per token and group of 128 columns, fp32 accumulation. No reference counterpart: the reference's fused_moe
+ * asserts that no scales are passed (nanovllm/layers/for_moe/fused_moe.py:248-249); the signature follows the
+ * block-quantised convention of its kernel arguments (A_scale / B_scale, block_shape [128, 128]).
+ *   x          bf16 [T, H]                      quantised inside (the bf16 input is not modified)
+ *   w13_q      e4m3 [E, 2*I, H] (one byte each), w13_scale fp32 [E, 2*I/128, H/128]
+ *   w2_q       e4m3 [E, H, I],                   w2_scale  fp32 [E, H/128, I/128]
+ *   out        bf16 [T, H]
+ * Requires H % 128 == 0 and I % 128 == 0 (I = the intermediate size held by this rank); SiLU only, no biases.
+ */
+size_t moe_b200_fused_experts_fp8_workspace_bytes(int T, int E, int top_k, int H, int I);
+int moe_b200_fused_experts_fp8(const void* x, const void* w13_q, const float* w13_scale, const void* w2_q,
+                               const float* w2_scale, const float* topk_weights, const int32_t* topk_ids, void* out,
+                               int T, int E, int top_k, int H, int I, void* workspace, size_t workspace_bytes,
+                               int32_t* status_word, void* stream);
+/* q[r, c] = e4m3(x[r, c] / s[r, c/128]), s[r, g] = max(|x[r, 128g .. 128g+127]|, 1e-10) / 448; x bf16 [rows, cols],
+ * cols % 128 == 0. The activation quantisation the call above applies (exposed for tests and for callers
+ * that keep quantised activations). */
+int moe_b200_quant_fp8_per_token_group(const void* x, int rows, int cols, void* q, float* scales, void* stream);
+
+/*
  * The two grouped GEMM passes on their own, for callers that keep the permutation (block size
  * moe_b200_block_m()) and the intermediates themselves. Each replaces one invoke_fused_moe_kernel call
  * of fused_experts_impl together with the element-wise kernel around it:

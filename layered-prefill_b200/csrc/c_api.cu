@@ -86,6 +86,32 @@ ExpertsWorkspace carve_experts(void* base, int T, int E, int top_k, int H, int I
   return w;
 }
 
+// fp8 path: the bf16 workspace plus the quantised copies of the hidden states and of the permuted intermediate.
+struct Fp8Workspace {
+  ExpertsWorkspace base;
+  uint8_t* x_q;
+  float* x_s;
+  uint8_t* h_q;
+  float* h_s;
+  size_t total;
+};
+
+Fp8Workspace carve_fp8(void* ws, int T, int E, int top_k, int H, int I) {
+  Fp8Workspace w;
+  w.base = carve_experts(ws, T, E, top_k, H, I);
+  const PermSizes ps = perm_sizes(T, E, top_k);
+  uint8_t* p = static_cast<uint8_t*>(ws);
+  size_t off = w.base.total;
+  const size_t rows_t = static_cast<size_t>(T > 0 ? T : 1);
+  const size_t rows_p = static_cast<size_t>(ps.sorted_cap > 0 ? ps.sorted_cap : 1);
+  w.x_q = p + off; off += align_up(rows_t * H);
+  w.x_s = reinterpret_cast<float*>(p + off); off += align_up(sizeof(float) * rows_t * ((H + 127) / 128));
+  w.h_q = p + off; off += align_up(rows_p * I);
+  w.h_s = reinterpret_cast<float*>(p + off); off += align_up(sizeof(float) * rows_p * ((I + 127) / 128));
+  w.total = off;
+  return w;
+}
+
 int check_block_shapes(int T, int E, int top_k, int H, int I) {
   if (T < 0 || E <= 0 || top_k <= 0 || top_k > E || H <= 0 || I <= 0)
     return set_error(kStatusInvalidArgument, "fused MoE: bad sizes T=%d E=%d k=%d H=%d I=%d", T, E, top_k, H, I);
@@ -275,6 +301,51 @@ int moe_b200_fused_experts(const void* x, const void* w13, const void* w2, const
     return st;
   return launch_moe_sum(experts_workspace_c3(workspace, T, E, top_k, H, I), static_cast<__nv_bfloat16*>(out), T, top_k,
                         H, s);
+}
+
+int moe_b200_quant_fp8_per_token_group(const void* x, int rows, int cols, void* q, float* scales, void* stream) {
+  if (x == nullptr || q == nullptr || scales == nullptr) return set_error(kStatusInvalidArgument, "quant_fp8_per_token_group: null pointer");
+  return launch_quant_rows_fp8(static_cast<const __nv_bfloat16*>(x), rows, cols, static_cast<uint8_t*>(q), scales, nullptr,
+                               0, nullptr, static_cast<cudaStream_t>(stream));
+}
+
+size_t moe_b200_fused_experts_fp8_workspace_bytes(int T, int E, int top_k, int H, int I) {
+  if (T < 0 || E <= 0 || top_k <= 0 || H <= 0 || I <= 0) return 0;
+  return carve_fp8(nullptr, T, E, top_k, H, I).total;
+}
+
+int moe_b200_fused_experts_fp8(const void* x, const void* w13_q, const float* w13_scale, const void* w2_q,
+                               const float* w2_scale, const float* topk_weights, const int32_t* topk_ids, void* out,
+                               int T, int E, int top_k, int H, int I, void* workspace, size_t workspace_bytes,
+                               int32_t* status_word, void* stream) {
+  if (int st = check_block_shapes(T, E, top_k, H, I)) return st;
+  if (H % 128 != 0 || I % 128 != 0)
+    return set_error(kStatusInvalidArgument, "fused_experts_fp8: H and the per-rank I must be multiples of 128 (H=%d I=%d)", H, I);
+  if (T == 0) return kStatusOk;
+  if (x == nullptr || w13_q == nullptr || w13_scale == nullptr || w2_q == nullptr || w2_scale == nullptr ||
+      topk_weights == nullptr || topk_ids == nullptr || out == nullptr || status_word == nullptr)
+    return set_error(kStatusInvalidArgument, "fused_experts_fp8: null pointer");
+  const size_t need = moe_b200_fused_experts_fp8_workspace_bytes(T, E, top_k, H, I);
+  if (workspace == nullptr || workspace_bytes < need)
+    return set_error(kStatusWorkspaceTooSmall, "fused_experts_fp8: workspace of %zu bytes needed, %zu given", need, workspace_bytes);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const Fp8Workspace w = carve_fp8(workspace, T, E, top_k, H, I);
+  const PermSizes ps = perm_sizes(T, E, top_k);
+  if (int st = launch_quant_rows_fp8(static_cast<const __nv_bfloat16*>(x), T, H, w.x_q, w.x_s, nullptr, 0, nullptr, s)) return st;
+  if (int st = launch_align_block_size(topk_ids, ps.numel, E, kBlockM, w.base.sorted_ids, ps.sorted_cap, w.base.expert_ids,
+                                       ps.blocks_cap, w.base.num_post_pad, w.base.align_ws, w.base.align_ws_bytes, s))
+    return st;
+  GroupedGemmArgs a{};
+  a.sorted_ids = w.base.sorted_ids; a.expert_ids = w.base.expert_ids; a.num_post_pad = w.base.num_post_pad;
+  a.numel = ps.numel; a.top_k = top_k; a.max_m_blocks = ps.blocks_cap; a.num_experts = E;
+  a.hidden = H; a.inter = I; a.activation = 0; a.status = status_word;
+  if (int st = launch_grouped_gemm1_fp8(a, w.x_q, w.x_s, static_cast<const uint8_t*>(w13_q), w13_scale, w.base.h_sorted, s)) return st;
+  if (int st = launch_quant_rows_fp8(w.base.h_sorted, ps.sorted_cap, I, w.h_q, w.h_s, w.base.sorted_ids, ps.numel,
+                                     w.base.num_post_pad, s))
+    return st;
+  if (int st = launch_grouped_gemm2_fp8(a, w.h_q, w.h_s, static_cast<const uint8_t*>(w2_q), w2_scale, topk_weights, w.base.c3, s))
+    return st;
+  return launch_moe_sum(w.base.c3, static_cast<__nv_bfloat16*>(out), T, top_k, H, s);
 }
 
 size_t moe_b200_fused_moe_workspace_bytes(int T, int E, int top_k, int H, int I) {

@@ -398,46 +398,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b, const KernelPara
 }
 
 // ---------------------------------------------------------------- host side
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_tiled_fn() {
-  static EncodeTiledFn fn = nullptr;
-  static bool tried = false;
-  if (!tried) {
-    tried = true;
-    void* sym = nullptr;
-    cudaDriverEntryPointQueryResult qres;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
-        qres == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(sym);
-  }
-  return fn;
-}
-
-// bf16 tensor, innermost dimension contiguous; dims/box given innermost first.
-int make_map(CUtensorMap* map, const void* base, int rank, const uint64_t* dims, const uint32_t* box) {
-  EncodeTiledFn fn = encode_tiled_fn();
-  if (fn == nullptr) return set_error(kStatusDriverEntryPoint, "cuTensorMapEncodeTiled is not available from this driver");
-  cuuint64_t gdim[3];
-  cuuint64_t gstride[2];
-  cuuint32_t bdim[3];
-  cuuint32_t estr[3] = {1, 1, 1};
-  uint64_t stride = 2;
-  for (int i = 0; i < rank; ++i) {
-    gdim[i] = dims[i];
-    bdim[i] = box[i];
-    stride *= dims[i];
-    if (i + 1 < rank) gstride[i] = stride;
-  }
-  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, static_cast<cuuint32_t>(rank), const_cast<void*>(base),
-                        gdim, gstride, bdim, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return set_error(kStatusCudaError, "cuTensorMapEncodeTiled failed with CUresult %d", static_cast<int>(r));
-  return kStatusOk;
-}
-
 template <int kMode>
 int ensure_smem_attr() {
   static bool done = false;
@@ -447,20 +407,6 @@ int ensure_smem_attr() {
     done = true;
   }
   return kStatusOk;
-}
-
-// Token blocks the permutation is expected to produce: experts hit at least once (each token picks
-// top_k distinct experts out of E) plus the full blocks of the busy ones. Only used to pick tile widths.
-double expected_m_blocks(int numel, int top_k, int num_experts) {
-  const double tokens = static_cast<double>(numel) / top_k;
-  const double miss = pow(1.0 - static_cast<double>(top_k) / num_experts, tokens);
-  return num_experts * (1.0 - miss) + static_cast<double>(numel) / BM;
-}
-
-// Fraction of SM-time doing work when `tiles` equal tiles are dealt round-robin to `sms` persistent CTAs.
-double wave_efficiency(double tiles, int sms) {
-  const double waves = ceil(tiles / sms);
-  return waves > 0 ? tiles / (waves * sms) : 1.0;
 }
 
 // Widest gate_up tile (output columns, a multiple of 16 dividing `inter`) among those within 2 % of the
@@ -504,6 +450,61 @@ int check_common(const GroupedGemmArgs& a) {
 
 }  // namespace
 
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+  }
+  return fn;
+}
+
+// Tensor map of a dense tensor (bf16, or bytes when elem_bytes == 1), innermost dimension contiguous, 128-byte
+// swizzle; dims/box given innermost first.
+int make_map(CUtensorMap* map, const void* base, int rank, const uint64_t* dims, const uint32_t* box, int elem_bytes) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (fn == nullptr) return set_error(kStatusDriverEntryPoint, "cuTensorMapEncodeTiled is not available from this driver");
+  cuuint64_t gdim[3];
+  cuuint64_t gstride[2];
+  cuuint32_t bdim[3];
+  cuuint32_t estr[3] = {1, 1, 1};
+  uint64_t stride = static_cast<uint64_t>(elem_bytes);
+  for (int i = 0; i < rank; ++i) {
+    gdim[i] = dims[i];
+    bdim[i] = box[i];
+    stride *= dims[i];
+    if (i + 1 < rank) gstride[i] = stride;
+  }
+  const CUresult r = fn(map, elem_bytes == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, static_cast<cuuint32_t>(rank), const_cast<void*>(base),
+                        gdim, gstride, bdim, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return set_error(kStatusCudaError, "cuTensorMapEncodeTiled failed with CUresult %d", static_cast<int>(r));
+  return kStatusOk;
+}
+
+// Token blocks the permutation is expected to produce: experts hit at least once (each token picks
+// top_k distinct experts out of E) plus the full blocks of the busy ones. Only used to pick tile widths.
+double expected_m_blocks(int numel, int top_k, int num_experts) {
+  const double tokens = static_cast<double>(numel) / top_k;
+  const double miss = pow(1.0 - static_cast<double>(top_k) / num_experts, tokens);
+  return num_experts * (1.0 - miss) + static_cast<double>(numel) / BM;
+}
+
+// Fraction of SM-time doing work when `tiles` equal tiles are dealt round-robin to `sms` persistent CTAs.
+double wave_efficiency(double tiles, int sms) {
+  const double waves = ceil(tiles / sms);
+  return waves > 0 ? tiles / (waves * sms) : 1.0;
+}
+
 int device_sm_count() {
   static int cached[64] = {0};
   int dev = 0;
@@ -527,7 +528,7 @@ int launch_grouped_gemm1(const GroupedGemmArgs& a, const __nv_bfloat16* x, const
   CUtensorMap map_b;
   const uint64_t dims[3] = {static_cast<uint64_t>(a.hidden), static_cast<uint64_t>(2 * a.inter), static_cast<uint64_t>(a.num_experts)};
   const uint32_t box[3] = {BK, static_cast<uint32_t>(a.activation == 1 ? mma_n : tile_cols), 1};
-  if (int st = make_map(&map_b, w13, 3, dims, box)) return st;
+  if (int st = make_map(&map_b, w13, 3, dims, box, 2)) return st;
 
   KernelParams p{};
   p.sorted_ids = a.sorted_ids; p.expert_ids = a.expert_ids; p.num_post_pad = a.num_post_pad;
@@ -562,7 +563,7 @@ int launch_grouped_gemm2(const GroupedGemmArgs& a, const __nv_bfloat16* h_sorted
   (void)rows_cap;
   const uint64_t dims_b[3] = {static_cast<uint64_t>(a.inter), static_cast<uint64_t>(a.hidden), static_cast<uint64_t>(a.num_experts)};
   const uint32_t box_b[3] = {BK, static_cast<uint32_t>(tile_cols), 1};
-  if (int st = make_map(&map_b, w2, 3, dims_b, box_b)) return st;
+  if (int st = make_map(&map_b, w2, 3, dims_b, box_b, 2)) return st;
 
   KernelParams p{};
   p.sorted_ids = a.sorted_ids; p.expert_ids = a.expert_ids; p.num_post_pad = a.num_post_pad;

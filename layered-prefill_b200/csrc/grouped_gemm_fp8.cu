@@ -1,0 +1,454 @@
+// fp8 (e4m3, w8a8) variant of the grouped expert GEMMs, block-scaled the way DeepSeek-style checkpoints are:
+//   weights      w_q [E, N, K] e4m3 with one fp32 scale per 128 x 128 block, w_s [E, ceil(N/128), K/128]
+//   activations  a_q [rows, K] e4m3 with one fp32 scale per row and group of 128 along K, a_s [rows, K/128],
+//                quantised on the fly (quant_rows_fp8_kernel: s = max(|x|, 1e-10) / 448, q = e4m3(x / s))
+//   C[r, n] = sum over K blocks kb of  a_s[r, kb] * w_s[n / 128, kb] * (a_q[r, kb-block] . w_q[n, kb-block])
+// The reference has no fp8 path (its fused_moe asserts the scales are None: for_moe/fused_moe.py:248-249), so
+// this follows the published block-quantisation scheme and is checked against a CPU emulation of it.
+//
+// Kernel: same skeleton as the bf16 kernels (grouped_gemm.cu): 128 permuted token rows per tile, weights by
+// TMA (byte tensor map, 128-byte swizzle), token rows by cp.async, one MMA thread, static tile list. What
+// differs: a shared-memory stage holds 128 K elements = exactly one scale block, so the tensor core cannot
+// accumulate across stages. Each stage's product (4 tcgen05.mma kind::f8f6f4, K = 32 each) goes into one of
+// two 128-column TMEM buffers, and eight warps (two per TMEM lane quarter, 64 accumulator columns each) read it
+// back, multiply by the two scales and accumulate in registers; the same warps then run the epilogue (SiLU * up
+// with the bf16 kernels' rounding points, or x routed weight). The first purpose is the weight-streaming
+// regime, where halving the bytes halves the time; at prefill sizes the register accumulation costs about as
+// much as the tensor cores save.
+#include <cuda_fp8.h>
+
+#include <cmath>
+#include <cstdio>
+
+#include "act_math.cuh"
+#include "launch.cuh"
+#include "moe_b200_internal.cuh"
+#include "ptx.cuh"
+
+namespace moe_b200 {
+
+namespace {
+
+constexpr int BM = kBlockM;
+constexpr int kGroup = 128;            // K elements per scale block = bytes per swizzle row = K per stage
+constexpr int kStageA = BM * kGroup;   // 16 KB of token rows
+constexpr int kStageB = 128 * kGroup;  // 16 KB of weight rows (64 gate + 64 up, or 128 down)
+constexpr int kStageBytes = kStageA + kStageB;
+constexpr int kStages = 6;
+constexpr int kPartCols = 128;         // accumulator columns per stage product
+constexpr int kTmemCols = 256;         // two of them
+constexpr int kBarrierBytes = 1024;
+constexpr int kSmemBytes = kBarrierBytes + 1024 /*alignment slack*/ + kStages * kStageBytes;
+
+constexpr int kWarpTma = 0;
+constexpr int kWarpMma = 1;
+constexpr int kWarpPromote0 = 2;  // 8 warps
+constexpr int kWarpGather0 = 10;  // 4 warps
+constexpr int kThreads = 448;
+
+struct ParamsF8 {
+  const int* sorted_ids;
+  const int* expert_ids;
+  const int* num_post_pad;
+  const uint8_t* a_q;  // [T, K] (gate_up: indexed by token) or [rows, K] (down: indexed by permuted row)
+  const float* a_s;    // [.., K / 128]
+  const float* w_s;    // [E, w_s_rows, K / 128]
+  int w_s_rows;
+  int numel;
+  int top_k;
+  int K;
+  int n_tiles;
+  int tile_cols;  // output columns per tile: 64 (gate_up) or 128 (down)
+  int out_cols;
+  int inter;      // row offset of the up half inside w13[e]
+  __nv_bfloat16* out;
+  long long out_ld;
+  const float* topk_w;
+  int* status;
+};
+
+union Pack8 {
+  uint4 u;
+  __nv_bfloat16 h[8];
+};
+
+__device__ __forceinline__ void report(int* status, int code) { atomicCAS(status, 0, code); }
+
+template <int kMode>  // 1 = gate_up, 2 = down
+__global__ void __launch_bounds__(kThreads, 1)
+grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_b, const ParamsF8 p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  uint64_t* bar_full = reinterpret_cast<uint64_t*>(smem);
+  uint64_t* bar_empty = bar_full + kStages;
+  uint64_t* bar_part_full = bar_empty + kStages;
+  uint64_t* bar_part_free = bar_part_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_part_free + 2);
+  uint8_t* ring = smem + kBarrierBytes;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&bar_full[s], 1 + 128);
+      mbar_init(&bar_empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&bar_part_full[b], 1);
+      mbar_init(&bar_part_free[b], 8);
+    }
+    fence_mbar_init();
+    tma_prefetch_desc(&tmap_b);
+  }
+  if (warp == kWarpMma) {
+    tmem_alloc(tmem_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  grid_dependency_launch();
+  grid_dependency_wait();
+
+  const int num_m_blocks = *p.num_post_pad / BM;
+  const int total_tiles = num_m_blocks * p.n_tiles;
+  const int num_kb = p.K / kGroup;
+
+  if (warp == kWarpTma) {
+    // ------------------------------------------------------------------ TMA producer (weights)
+    if (lane == 0) {
+      uint32_t s = 0, ph = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        const int m_blk = tile / p.n_tiles;
+        const int n0 = (tile % p.n_tiles) * p.tile_cols;
+        const int e = p.expert_ids[m_blk];
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&bar_empty[s], ph ^ 1u)) {
+            report(p.status, kErrWaitEmpty);
+            ok = false;
+            break;
+          }
+          uint8_t* b_dst = ring + s * kStageBytes + kStageA;
+          mbar_arrive_expect_tx(&bar_full[s], kStageB);
+          if (kMode == 1) {
+            tma_load_3d(b_dst, &tmap_b, kb * kGroup, n0, e, &bar_full[s]);
+            tma_load_3d(b_dst + 64 * kGroup, &tmap_b, kb * kGroup, p.inter + n0, e, &bar_full[s]);
+          } else {
+            tma_load_3d(b_dst, &tmap_b, kb * kGroup, n0, e, &bar_full[s]);
+          }
+          if (++s == kStages) {
+            s = 0;
+            ph ^= 1u;
+          }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == kWarpMma) {
+    // ------------------------------------------------------------------ MMA issuer: one stage = one product buffer
+    if (lane == 0) {
+      const uint32_t idesc = umma_idesc_e4m3(BM, kPartCols);
+      uint32_t s = 0, ph = 0, j = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        for (int kb = 0; kb < num_kb; ++kb, ++j) {
+          const uint32_t b = j & 1u;
+          const uint32_t bph = (j >> 1) & 1u;
+          if (!mbar_wait(&bar_part_free[b], bph ^ 1u)) {
+            report(p.status, kErrWaitTmemEmpty);
+            ok = false;
+            break;
+          }
+          if (!mbar_wait(&bar_full[s], ph)) {
+            report(p.status, kErrWaitFull);
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t a_addr = smem_u32(ring + s * kStageBytes);
+          const uint64_t adesc = umma_desc_k_sw128(a_addr);
+          const uint64_t bdesc = umma_desc_k_sw128(a_addr + kStageA);
+          const uint32_t d_tmem = tmem_base + b * kPartCols;
+          // 32 e4m3 = 32 bytes along K per instruction: +2 in the descriptor's 16-byte units
+          umma_e4m3(d_tmem, adesc, bdesc, idesc, 0u);
+          umma_e4m3(d_tmem, adesc + 2, bdesc + 2, idesc, 1u);
+          umma_e4m3(d_tmem, adesc + 4, bdesc + 4, idesc, 1u);
+          umma_e4m3(d_tmem, adesc + 6, bdesc + 6, idesc, 1u);
+          umma_commit(&bar_empty[s]);
+          umma_commit(&bar_part_full[b]);
+          if (++s == kStages) {
+            s = 0;
+            ph ^= 1u;
+          }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp >= kWarpPromote0 && warp < kWarpPromote0 + 8) {
+    // ------------------------------------------------------------------ scale-and-accumulate, then epilogue
+    const int q = warp & 3;                        // TMEM lane quarter this warp may read
+    const int hf = (warp - kWarpPromote0) >> 2;    // which half of the tile's output columns
+    const int row_in_tile = q * 32 + lane;
+    const int scale_ld = p.K / kGroup;
+    uint32_t j = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      const int m_blk = tile / p.n_tiles;
+      const int n0 = (tile % p.n_tiles) * p.tile_cols;
+      const int e = p.expert_ids[m_blk];
+      const long long pos = static_cast<long long>(m_blk) * BM + row_in_tile;
+      const int flat = p.sorted_ids[pos];
+      const bool valid = flat < p.numel;
+      const bool any_valid = __any_sync(0xffffffffu, valid);
+      const float* a_s_row =
+          p.a_s + (kMode == 1 ? static_cast<long long>(valid ? flat / p.top_k : 0) : (valid ? pos : 0)) * scale_ld;
+      const float* w_s0 = p.w_s + (static_cast<long long>(e) * p.w_s_rows + n0 / kGroup) * scale_ld;
+      const float* w_s1 = p.w_s + (static_cast<long long>(e) * p.w_s_rows + (p.inter + n0) / kGroup) * scale_ld;
+
+      float acc[64];
+#pragma unroll
+      for (int i = 0; i < 64; ++i) acc[i] = 0.f;
+
+      for (int kb = 0; kb < num_kb; ++kb, ++j) {
+        const uint32_t b = j & 1u;
+        const uint32_t bph = (j >> 1) & 1u;
+        const float sa = valid ? a_s_row[kb] : 0.f;
+        const float s0 = sa * __ldg(w_s0 + kb);
+        const float s1 = kMode == 1 ? sa * __ldg(w_s1 + kb) : s0;
+        ok = mbar_wait(&bar_part_full[b], bph);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) {
+          if (lane == 0) report(p.status, kErrWaitTmemFull);
+          break;
+        }
+        tc_fence_after_sync();
+        if (any_valid) {
+          const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + b * kPartCols;
+          // gate_up: columns [32 hf, +32) of the gate half and of the up half (at +64); down: columns [64 hf, +64)
+          const uint32_t c0 = kMode == 1 ? 32u * hf : 64u * hf;
+          const uint32_t c1 = kMode == 1 ? 64u + 32u * hf : 64u * hf + 32u;
+          uint32_t v0[16], v1[16];
+          tmem_ld_x16(taddr + c0, v0);
+          tmem_ld_x16(taddr + c0 + 16, v1);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            acc[i] = fmaf(__uint_as_float(v0[i]), s0, acc[i]);
+            acc[16 + i] = fmaf(__uint_as_float(v1[i]), s0, acc[16 + i]);
+          }
+          tmem_ld_x16(taddr + c1, v0);
+          tmem_ld_x16(taddr + c1 + 16, v1);
+          tmem_ld_wait();
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&bar_part_free[b]);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            acc[32 + i] = fmaf(__uint_as_float(v0[i]), s1, acc[32 + i]);
+            acc[48 + i] = fmaf(__uint_as_float(v1[i]), s1, acc[48 + i]);
+          }
+        } else {
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&bar_part_free[b]);
+        }
+      }
+      if (!ok) break;
+
+      if (valid) {
+        if (kMode == 1) {
+          // acc[0..31] = gate columns n0 + 32 hf + i, acc[32..63] = the matching up columns
+          __nv_bfloat16* dst = p.out + pos * p.out_ld + n0 + 32 * hf;
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            Pack8 o;
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              o.h[i] = silu_mul_bf16_fast(__float2bfloat16_rn(acc[8 * v + i]), __float2bfloat16_rn(acc[32 + 8 * v + i]));
+            if (n0 + 32 * hf + 8 * v < p.out_cols) *reinterpret_cast<uint4*>(dst + 8 * v) = o.u;
+          }
+        } else {
+          const float w = p.topk_w[flat];
+          __nv_bfloat16* dst = p.out + static_cast<long long>(flat) * p.out_ld + n0 + 64 * hf;
+#pragma unroll
+          for (int v = 0; v < 8; ++v) {
+            Pack8 o;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) o.h[i] = __float2bfloat16_rn(acc[8 * v + i] * w);
+            if (n0 + 64 * hf + 8 * v < p.out_cols) *reinterpret_cast<uint4*>(dst + 8 * v) = o.u;
+          }
+        }
+      }
+    }
+  } else if (warp >= kWarpGather0) {
+    // ------------------------------------------------------------------ token-row gather (128 bytes per row and stage)
+    const int gw = warp - kWarpGather0;
+    const int sub = lane >> 3;
+    const int ch = lane & 7;
+    const int row0 = gw * 4 + sub;
+    const uint32_t swz = static_cast<uint32_t>((ch ^ (row0 & 7)) << 4);
+    uint32_t s = 0, ph = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      const int m_blk = tile / p.n_tiles;
+      const uint8_t* src[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const long long pos = static_cast<long long>(m_blk) * BM + row0 + 16 * i;
+        const int flat = p.sorted_ids[pos];
+        if (kMode == 1)
+          src[i] = flat < p.numel ? p.a_q + static_cast<long long>(flat / p.top_k) * p.K + ch * 16 : nullptr;
+        else
+          src[i] = flat < p.numel ? p.a_q + pos * p.K + ch * 16 : nullptr;
+      }
+      for (int kb = 0; kb < num_kb; ++kb) {
+        ok = mbar_wait(&bar_empty[s], ph ^ 1u);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) {
+          if (lane == 0) report(p.status, kErrWaitEmpty);
+          break;
+        }
+        const uint32_t a_base = smem_u32(ring + s * kStageBytes);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const uint32_t dst = a_base + static_cast<uint32_t>(row0 + 16 * i) * 128u + swz;
+          const bool live = src[i] != nullptr;
+          cp_async_16(dst, live ? static_cast<const void*>(src[i] + kb * kGroup) : static_cast<const void*>(p.a_q),
+                      live ? 16u : 0u);
+        }
+        cp_async_mbar_arrive_noinc(&bar_full[s]);
+        if (++s == kStages) {
+          s = 0;
+          ph ^= 1u;
+        }
+      }
+    }
+    cp_async_wait_all();
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  if (warp == kWarpMma) tmem_dealloc(tmem_base, kTmemCols);
+}
+
+// One warp per (row, group of 128 columns): 4 values per lane.
+__global__ void __launch_bounds__(256)
+quant_rows_fp8_kernel(const __nv_bfloat16* __restrict__ x, int rows, int cols, uint8_t* __restrict__ q,
+                      float* __restrict__ s, const int* __restrict__ sorted_ids, int numel,
+                      const int* __restrict__ num_post_pad) {
+  grid_dependency_launch();
+  grid_dependency_wait();
+  const int groups = cols / kGroup;
+  const long long w = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (w >= static_cast<long long>(rows) * groups) return;
+  const int row = static_cast<int>(w / groups);
+  const int g = static_cast<int>(w % groups);
+  if (sorted_ids != nullptr && (row >= *num_post_pad || sorted_ids[row] >= numel)) return;  // padding row
+  const __nv_bfloat16* src = x + static_cast<long long>(row) * cols + g * kGroup + lane * 4;
+  const uint2 raw = *reinterpret_cast<const uint2*>(src);
+  const __nv_bfloat162 p0 = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
+  const __nv_bfloat162 p1 = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+  const float v[4] = {__low2float(p0), __high2float(p0), __low2float(p1), __high2float(p1)};
+  float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, d));
+  const float scale = fmaxf(amax, 1e-10f) / 448.0f;
+  uint32_t packed = 0;
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+    packed |= static_cast<uint32_t>(__nv_cvt_float_to_fp8(v[i] / scale, __NV_SATFINITE, __NV_E4M3)) << (8 * i);
+  *reinterpret_cast<uint32_t*>(q + static_cast<long long>(row) * cols + g * kGroup + lane * 4) = packed;
+  if (lane == 0) s[static_cast<long long>(row) * groups + g] = scale;
+}
+
+template <int kMode>
+int ensure_smem_attr_f8() {
+  static bool done = false;
+  if (!done) {
+    const cudaError_t e = cudaFuncSetAttribute(grouped_gemm_fp8_kernel<kMode>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    if (e != cudaSuccess) return check_cuda(e, "cudaFuncSetAttribute(grouped_gemm_fp8_kernel)");
+    done = true;
+  }
+  return kStatusOk;
+}
+
+int check_fp8_shapes(const GroupedGemmArgs& a) {
+  if (a.hidden <= 0 || a.inter <= 0 || a.hidden % kGroup != 0 || a.inter % kGroup != 0)
+    return set_error(kStatusInvalidArgument, "fp8 grouped GEMM: hidden and the per-rank intermediate size must be multiples of %d (got %d, %d)", kGroup, a.hidden, a.inter);
+  if (a.top_k <= 0 || a.numel < 0 || a.max_m_blocks < 0 || a.status == nullptr)
+    return set_error(kStatusInvalidArgument, "fp8 grouped GEMM: bad routing sizes or null status word");
+  if (a.activation != 0) return set_error(kStatusInvalidArgument, "fp8 grouped GEMM: only the silu activation is built");
+  return kStatusOk;
+}
+
+}  // namespace
+
+int launch_quant_rows_fp8(const __nv_bfloat16* x, int rows, int cols, uint8_t* q, float* s, const int* sorted_ids,
+                          int numel, const int* num_post_pad, cudaStream_t stream) {
+  if (rows < 0 || cols <= 0 || cols % kGroup != 0)
+    return set_error(kStatusInvalidArgument, "fp8 quantisation: the row length must be a multiple of %d (got %d)", kGroup, cols);
+  if (rows == 0) return kStatusOk;
+  const long long warps = static_cast<long long>(rows) * (cols / kGroup);
+  const unsigned blocks = static_cast<unsigned>((warps + 7) / 8);
+  if (int st = check_cuda(launch_pdl(quant_rows_fp8_kernel, dim3(blocks), dim3(256), 0, stream, x, rows, cols, q, s,
+                                     sorted_ids, numel, num_post_pad),
+                          "quant_rows_fp8 launch"))
+    return st;
+  count_launches(1);
+  return check_launch("quant_rows_fp8");
+}
+
+int launch_grouped_gemm1_fp8(const GroupedGemmArgs& a, const uint8_t* x_q, const float* x_s, const uint8_t* w13_q,
+                             const float* w13_s, __nv_bfloat16* h_sorted, cudaStream_t stream) {
+  if (int st = check_fp8_shapes(a)) return st;
+  if (a.numel == 0 || a.max_m_blocks == 0) return kStatusOk;
+  if (int st = ensure_smem_attr_f8<1>()) return st;
+  CUtensorMap map_b;
+  const uint64_t dims[3] = {static_cast<uint64_t>(a.hidden), static_cast<uint64_t>(2 * a.inter), static_cast<uint64_t>(a.num_experts)};
+  const uint32_t box[3] = {kGroup, 64, 1};
+  if (int st = make_map(&map_b, w13_q, 3, dims, box, 1)) return st;
+  ParamsF8 p{};
+  p.sorted_ids = a.sorted_ids; p.expert_ids = a.expert_ids; p.num_post_pad = a.num_post_pad;
+  p.a_q = x_q; p.a_s = x_s; p.w_s = w13_s; p.w_s_rows = (2 * a.inter + kGroup - 1) / kGroup;
+  p.numel = a.numel; p.top_k = a.top_k; p.K = a.hidden;
+  p.tile_cols = 64; p.n_tiles = a.inter / 64; p.out_cols = a.inter; p.inter = a.inter;
+  p.out = h_sorted; p.out_ld = a.inter; p.topk_w = nullptr; p.status = a.status;
+  const long long tiles = static_cast<long long>(a.max_m_blocks) * p.n_tiles;
+  const int grid = static_cast<int>(tiles < device_sm_count() ? tiles : device_sm_count());
+  if (int st = check_cuda(launch_pdl(grouped_gemm_fp8_kernel<1>, dim3(grid), dim3(kThreads), kSmemBytes, stream, map_b, p),
+                          "grouped_gemm_fp8 gate_up launch"))
+    return st;
+  count_launches(1);
+  return check_launch("grouped_gemm_fp8 gate_up");
+}
+
+int launch_grouped_gemm2_fp8(const GroupedGemmArgs& a, const uint8_t* h_q, const float* h_s, const uint8_t* w2_q,
+                             const float* w2_s, const float* topk_w, __nv_bfloat16* c3, cudaStream_t stream) {
+  if (int st = check_fp8_shapes(a)) return st;
+  if (a.numel == 0 || a.max_m_blocks == 0) return kStatusOk;
+  if (int st = ensure_smem_attr_f8<2>()) return st;
+  CUtensorMap map_b;
+  const uint64_t dims[3] = {static_cast<uint64_t>(a.inter), static_cast<uint64_t>(a.hidden), static_cast<uint64_t>(a.num_experts)};
+  const uint32_t box[3] = {kGroup, 128, 1};
+  if (int st = make_map(&map_b, w2_q, 3, dims, box, 1)) return st;
+  ParamsF8 p{};
+  p.sorted_ids = a.sorted_ids; p.expert_ids = a.expert_ids; p.num_post_pad = a.num_post_pad;
+  p.a_q = h_q; p.a_s = h_s; p.w_s = w2_s; p.w_s_rows = (a.hidden + kGroup - 1) / kGroup;
+  p.numel = a.numel; p.top_k = a.top_k; p.K = a.inter;
+  p.tile_cols = 128; p.n_tiles = a.hidden / 128; p.out_cols = a.hidden; p.inter = 0;
+  p.out = c3; p.out_ld = a.hidden; p.topk_w = topk_w; p.status = a.status;
+  const long long tiles = static_cast<long long>(a.max_m_blocks) * p.n_tiles;
+  const int grid = static_cast<int>(tiles < device_sm_count() ? tiles : device_sm_count());
+  if (int st = check_cuda(launch_pdl(grouped_gemm_fp8_kernel<2>, dim3(grid), dim3(kThreads), kSmemBytes, stream, map_b, p),
+                          "grouped_gemm_fp8 down launch"))
+    return st;
+  count_launches(1);
+  return check_launch("grouped_gemm_fp8 down");
+}
+
+}  // namespace moe_b200

@@ -79,4 +79,19 @@ int launch_grouped_gemm2(const GroupedGemmArgs& a, const __nv_bfloat16* h_sorted
                          __nv_bfloat16* c3, cudaStream_t stream);
 int device_sm_count();
 
+// ---- grouped_gemm_fp8.cu (e4m3 weights with 128 x 128 block scales, activations quantised per row and 128 columns)
+// q[r, c] = e4m3(x[r, c] / s[r, c / 128]), s = max(|x| over the group, 1e-10) / 448. With sorted_ids given, rows that are
+// padding of the permutation (or lie beyond *num_post_pad) are skipped.
+int launch_quant_rows_fp8(const __nv_bfloat16* x, int rows, int cols, uint8_t* q, float* s, const int* sorted_ids,
+                          int numel, const int* num_post_pad, cudaStream_t stream);
+int launch_grouped_gemm1_fp8(const GroupedGemmArgs& a, const uint8_t* x_q, const float* x_s, const uint8_t* w13_q,
+                             const float* w13_s, __nv_bfloat16* h_sorted, cudaStream_t stream);
+int launch_grouped_gemm2_fp8(const GroupedGemmArgs& a, const uint8_t* h_q, const float* h_s, const uint8_t* w2_q,
+                             const float* w2_s, const float* topk_w, __nv_bfloat16* c3, cudaStream_t stream);
+// Tensor map of a dense bf16 (elem_bytes 2) or byte (elem_bytes 1) tensor, 128-byte swizzle; dims/box innermost first.
+int make_map(CUtensorMap* map, const void* base, int rank, const uint64_t* dims, const uint32_t* box, int elem_bytes);
+// Token blocks the permutation is expected to produce, and the share of SM-time a round-robin tile list keeps busy.
+double expected_m_blocks(int numel, int top_k, int num_experts);
+double wave_efficiency(double tiles, int sms);
+
 }  // namespace moe_b200

@@ -96,7 +96,12 @@ def fused_experts_impl(hidden_states: torch.Tensor, w1: torch.Tensor, w2: torch.
                        w1_scale=None, w2_scale=None, w1_zp=None, w2_zp=None, a1_scale=None, a2_scale=None,
                        block_shape=None, w1_bias: Optional[torch.Tensor] = None,
                        w2_bias: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """for_moe/fused_moe.py:461-633."""
+    """for_moe/fused_moe.py:461-633. With e4m3 weights, `w1_scale` / `w2_scale` and `block_shape=[128, 128]` (arguments
+    the reference declares and asserts unused) the block-scaled fp8 path runs instead."""
+    if w1.dtype in (torch.float8_e4m3fn, torch.uint8):
+        return _fused_experts_fp8(hidden_states, w1, w2, topk_weights, topk_ids, inplace, activation, w1_scale,
+                                  w2_scale, block_shape, w1_bias, w2_bias, a1_scale, a2_scale, w1_zp, w2_zp,
+                                  expert_map, apply_router_weight_on_input)
     _check_experts_args(hidden_states, w1, w2, topk_weights, topk_ids, activation, w1_scale=w1_scale,
                         w2_scale=w2_scale, w1_zp=w1_zp, w2_zp=w2_zp, a1_scale=a1_scale, a2_scale=a2_scale,
                         block_shape=block_shape, expert_map=expert_map)
@@ -124,6 +129,73 @@ def fused_experts_impl(hidden_states: torch.Tensor, w1: torch.Tensor, w2: torch.
             tw.data_ptr(), ti.data_ptr(), out.data_ptr(), T, E, k, H, inter, ACT_CODES[activation],
             ws.data_ptr(), ws.numel(), ops.status_word(dev).data_ptr(), torch.cuda.current_stream().cuda_stream))
     return out
+
+
+def _fused_experts_fp8(hidden_states, w1, w2, topk_weights, topk_ids, inplace, activation, w1_scale, w2_scale,
+                       block_shape, w1_bias, w2_bias, a1_scale, a2_scale, w1_zp, w2_zp, expert_map,
+                       apply_router_weight_on_input) -> torch.Tensor:
+    """w8a8 e4m3: weights [E, 2I, H] / [E, H, I] with fp32 scales per 128 x 128 block, activations quantised per
+    token and 128 columns inside the library (dynamic, so a1_scale / a2_scale stay None)."""
+    if not hidden_states.is_cuda:
+        raise RuntimeError("fused_experts needs CUDA tensors; there is no CPU path")
+    if hidden_states.dtype != torch.bfloat16:
+        raise ValueError(f"Unsupported compute_type: {hidden_states.dtype} (activations enter as bfloat16)")
+    if w2.dtype != w1.dtype:
+        raise ValueError("w1 and w2 must both be e4m3")
+    if w1_scale is None or w2_scale is None or block_shape is None or list(block_shape) != [128, 128]:
+        raise ValueError("fp8 weights need w1_scale, w2_scale and block_shape=[128, 128]")
+    if activation != "silu" or w1_bias is not None or w2_bias is not None:
+        raise NotImplementedError("the fp8 path is built for silu without expert biases")
+    for name, v in dict(a1_scale=a1_scale, a2_scale=a2_scale, w1_zp=w1_zp, w2_zp=w2_zp, expert_map=expert_map).items():
+        assert v is None, f"{name} is not supported"
+    if apply_router_weight_on_input:
+        raise NotImplementedError("apply_router_weight_on_input=True is not used by the reference's models")
+    assert hidden_states.is_contiguous() and w1.is_contiguous() and w2.is_contiguous()
+    T, H = hidden_states.shape
+    E, two_i, _ = w1.shape
+    inter = two_i // 2
+    assert w1.shape == (E, 2 * inter, H) and w2.shape == (E, H, inter)
+    if H % 128 or inter % 128:
+        raise ValueError(f"fp8 path needs H and I to be multiples of 128 (H={H}, I={inter})")
+    s1 = w1_scale.to(torch.float32).contiguous()
+    s2 = w2_scale.to(torch.float32).contiguous()
+    assert s1.shape == (E, 2 * inter // 128, H // 128), f"w1_scale shape {tuple(s1.shape)}"
+    assert s2.shape == (E, H // 128, inter // 128), f"w2_scale shape {tuple(s2.shape)}"
+    k = topk_ids.size(1)
+    out = hidden_states if inplace else torch.empty_like(hidden_states)
+    if T == 0:
+        return out
+    tw = topk_weights.to(torch.float32).contiguous()
+    ti = topk_ids.to(torch.int32).contiguous()
+    dev = hidden_states.device
+    nbytes = lib.moe_b200_fused_experts_fp8_workspace_bytes(T, E, k, H, inter)
+    ws = _workspaces.get(dev, nbytes)
+    import ctypes
+    fptr = ctypes.POINTER(ctypes.c_float)
+    with torch.cuda.device(dev):
+        check(lib.moe_b200_fused_experts_fp8(
+            hidden_states.data_ptr(), w1.data_ptr(), ctypes.cast(s1.data_ptr(), fptr), w2.data_ptr(),
+            ctypes.cast(s2.data_ptr(), fptr), tw.data_ptr(), ti.data_ptr(), out.data_ptr(), T, E, k, H, inter,
+            ws.data_ptr(), ws.numel(), ops.status_word(dev).data_ptr(), torch.cuda.current_stream().cuda_stream))
+    return out
+
+
+def per_token_group_quant_fp8(x: torch.Tensor, group_size: int = 128):
+    """x bf16 [rows, cols] -> (e4m3 [rows, cols], fp32 scales [rows, cols / 128]); the quantisation the fp8 path
+    applies to its activations."""
+    if group_size != 128:
+        raise ValueError("group_size must be 128")
+    if not x.is_cuda:
+        raise RuntimeError("per_token_group_quant_fp8 needs a CUDA tensor; there is no CPU path")
+    assert x.dtype == torch.bfloat16 and x.dim() == 2 and x.is_contiguous() and x.size(1) % 128 == 0
+    q = torch.empty(x.shape, dtype=torch.float8_e4m3fn, device=x.device)
+    s = torch.empty((x.size(0), x.size(1) // 128), dtype=torch.float32, device=x.device)
+    import ctypes
+    with torch.cuda.device(x.device):
+        check(lib.moe_b200_quant_fp8_per_token_group(
+            x.data_ptr(), x.size(0), x.size(1), q.data_ptr(), ctypes.cast(s.data_ptr(), ctypes.POINTER(ctypes.c_float)),
+            torch.cuda.current_stream().cuda_stream))
+    return q, s
 
 
 def fused_experts(hidden_states: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor, w1_bias: Optional[torch.Tensor],

@@ -1,0 +1,101 @@
+"""The e4m3 block-scaled path (fused_experts with w1_scale / w2_scale / block_shape=[128, 128]).
+
+The reference has no fp8 path, so there is nothing of its own to pin against: the checker is the CPU emulation of
+the same quantisation scheme (oracle.fused_experts_fp8), itself tied to the bf16 oracle on dequantised weights.
+Tolerances: rel-L2 <= 5e-3 against the emulation (same quantised operands, fp32 accumulation in another order);
+rel-L2 <= 8e-2 against bf16 math on the dequantised weights (that distance is the activation quantisation:
+e4m3 keeps 3 mantissa bits, and it is applied to x and to the intermediate)."""
+import pytest
+import torch
+
+from oracle import moe_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+REL_L2_EMULATION = 5e-3
+REL_L2_DEQUANT = 8e-2
+
+
+def _dev():
+    return torch.device("cuda", 0)
+
+
+def _status_ok():
+    from layered_prefill_b200 import ops
+    assert ops.read_status(_dev()) == 0, "a device-side wait timed out"
+
+
+@pytest.mark.parametrize("rows,cols", [(1, 128), (7, 256), (130, 2048), (64, 768)])
+def test_activation_quantisation_is_bit_exact(rows, cols):
+    from layered_prefill_b200 import fused_moe
+    g = torch.Generator().manual_seed(rows + cols)
+    x = (torch.randn(rows, cols, generator=g) * 3).to(torch.bfloat16)
+    x[0, :128] = 0                      # an all-zero group: scale clamps at 1e-10 / 448
+    if rows > 2:
+        x[2, 5] = 1000.0                # one outlier sets its group's scale
+    q, s = fused_moe.per_token_group_quant_fp8(x.to(_dev()))
+    oq, os_ = O.per_token_group_quant_fp8(x)
+    assert torch.equal(s.cpu(), os_)
+    assert torch.equal(q.cpu().view(torch.uint8), oq.view(torch.uint8))
+
+
+def _case(T, H, E, k, I, seed, skew=0.0, given_scales=False):
+    from layered_prefill_b200 import fused_moe
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(T, H, generator=g).to(torch.bfloat16)
+    w13 = (torch.randn(E, 2 * I, H, generator=g) * 0.02).to(torch.bfloat16)
+    w2 = (torch.randn(E, H, I, generator=g) * 0.02).to(torch.bfloat16)
+    s13 = s2 = None
+    if given_scales:  # the benchmark config's recipe: scales ~ U(0.5, 2) / 448, masters quantised with them
+        s13 = (torch.rand(E, 2 * I // 128, H // 128, generator=g) * 1.5 + 0.5) / 448
+        s2 = (torch.rand(E, H // 128, I // 128, generator=g) * 1.5 + 0.5) / 448
+    q13, s13 = O.quant_weight_block_fp8(w13, s13)
+    q2, s2 = O.quant_weight_block_fp8(w2, s2)
+    logits = torch.randn(T, E, generator=g) + skew * torch.randn(E, generator=g)
+    tw, ti, _ = O.fused_topk(x, logits, k, True)
+    want = O.fused_experts_fp8(x, q13, s13, q2, s2, tw, ti)
+    d = _dev()
+    got = fused_moe.fused_experts(x.to(d), q13.to(d), q2.to(d), None, None, tw.to(d), ti.to(d), inplace=False,
+                                  w1_scale=s13.to(d), w2_scale=s2.to(d), block_shape=[128, 128]).cpu()
+    _status_ok()
+    assert torch.isfinite(got.float()).all()
+    assert O.rel_l2(got, want) <= REL_L2_EMULATION, (O.rel_l2(got, want), O.max_abs(got, want))
+    deq = O.fused_experts(x, O.dequant_weight_block_fp8(q13, s13).to(torch.bfloat16),
+                          O.dequant_weight_block_fp8(q2, s2).to(torch.bfloat16), tw, ti, "silu", "exact")
+    assert O.rel_l2(got, deq) <= REL_L2_DEQUANT, O.rel_l2(got, deq)
+    return got
+
+
+@pytest.mark.parametrize("T,H,E,k,I", [
+    (1, 128, 4, 1, 128),       # smallest legal shapes: one scale block everywhere
+    (40, 256, 4, 2, 128),
+    (130, 256, 8, 2, 256),     # more than one 128-row block per expert, two gate_up column tiles per half
+    (64, 512, 16, 4, 384),     # three K blocks in the down pass
+    (300, 384, 4, 2, 128),     # H = 3 scale blocks: odd number of stage products per tile
+])
+def test_fp8_experts_small_shapes(T, H, E, k, I):
+    _case(T, H, E, k, I, seed=T + I)
+
+
+def test_fp8_experts_imbalanced_routing_and_given_scales():
+    _case(500, 256, 8, 2, 128, seed=9, skew=3.0, given_scales=True)
+
+
+def test_fp8_experts_at_the_benchmark_width():
+    """Qwen3-30B-A3B's H and I at decode size, a quarter of its experts (the CPU emulation quantises every weight)."""
+    _case(64, 2048, 32, 8, 768, seed=11, given_scales=True)
+
+
+def test_fp8_rejects_what_it_does_not_build():
+    from layered_prefill_b200 import fused_moe
+    d = _dev()
+    x = torch.zeros(4, 192, dtype=torch.bfloat16, device=d)
+    w13 = torch.zeros(2, 256, 192, dtype=torch.float8_e4m3fn, device=d)
+    w2 = torch.zeros(2, 192, 128, dtype=torch.float8_e4m3fn, device=d)
+    tw = torch.ones(4, 1, device=d)
+    ti = torch.zeros(4, 1, dtype=torch.int32, device=d)
+    with pytest.raises(ValueError):   # H not a multiple of 128
+        fused_moe.fused_experts(x, w13, w2, None, None, tw, ti, w1_scale=torch.ones(2, 2, 2, device=d),
+                                w2_scale=torch.ones(2, 2, 1, device=d), block_shape=[128, 128])
+    with pytest.raises(ValueError):   # scales missing
+        fused_moe.fused_experts(x, w13, w2, None, None, tw, ti)
