@@ -138,6 +138,9 @@ def build_parser():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--weight-sets", type=int, default=4, help="distinct weight copies rotated through (L2 defeat)")
     ap.add_argument("--tokens", type=int, default=None, help="override the workload's token count (profiling)")
+    ap.add_argument("--fp8", action="store_true",
+                    help="e4m3 block-scaled weights (scales ~ U(0.5, 2) / 448 per 128 x 128 block) and per-token-group "
+                         "activation quantisation instead of bf16; 1 GPU")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true",
                     help="launch every step eagerly (default: decode-sized steps replay a captured CUDA graph, as the "
@@ -260,6 +263,8 @@ def main():
         if comm.disabled:
             raise SystemExit("peer-memory all-reduce could not be initialised on this box")
 
+    if args.fp8 and (world > 1 or mixed):
+        raise SystemExit("--fp8 runs the single-GPU block only")
     prefill = wl.T >= 2048
     steps = args.steps if args.steps is not None else (20 if mixed else 200 if prefill else 2000)
     warmup = args.warmup if args.warmup is not None else (3 if mixed else 10 if prefill else 50)
@@ -284,7 +289,17 @@ def main():
         g.manual_seed(1000 + s)
         w13_full = (torch.randn(wl.E, 2 * wl.I, wl.H, generator=g, device=dev, dtype=torch.float32) * 0.02).to(torch.bfloat16)
         w2_full = (torch.randn(wl.E, wl.H, wl.I, generator=g, device=dev, dtype=torch.float32) * 0.02).to(torch.bfloat16)
-        if tp == 1:
+        if args.fp8:
+            def quantise(w):  # masters quantised with drawn scales, as the benchmark config describes
+                e, n, k = w.shape
+                sc = (torch.rand(e, n // 128, k // 128, generator=g, device=dev) * 1.5 + 0.5) / 448.0
+                blocks = w.float().view(e, n // 128, 128, k // 128, 128) / sc[:, :, None, :, None]
+                return blocks.clamp(-448, 448).to(torch.float8_e4m3fn).view(e, n, k).contiguous(), sc
+            q13, s13 = quantise(w13_full)
+            q2, s2 = quantise(w2_full)
+            sets.append((q13, q2, s13, s2))
+            del w13_full, w2_full
+        elif tp == 1:
             sets.append((w13_full, w2_full))
         else:
             lo, hi = rank * ip, (rank + 1) * ip
@@ -295,6 +310,9 @@ def main():
     out = torch.empty_like(x)
 
     def block(i, xin, lgin, dst):
+        if args.fp8:
+            q13, q2, s13, s2 = sets[i % n_sets]
+            return fused_moe.fused_moe_forward_fp8(xin, lgin, q13, s13, q2, s2, wl.top_k, True, out=dst)
         w13, w2 = sets[i % n_sets]
         return fused_moe.fused_moe_forward(xin, lgin, w13, w2, wl.top_k, True, "silu", inplace=False, comm=comm,
                                            out=dst)
@@ -480,6 +498,8 @@ def main():
     stream = torch.cuda.current_stream().cuda_stream
 
     def gate_up(i):
+        if args.fp8:
+            return
         w13, _ = sets[i % n_sets]
         rc = lib.moe_b200_grouped_gemm_gate_up(x.data_ptr(), w13.data_ptr(), 0, s_pad.data_ptr(), e_ids.data_ptr(),
                                                post.data_ptr(), h_sorted.data_ptr(), rows_cap, wl.T, wl.E, wl.top_k,
@@ -497,7 +517,7 @@ def main():
         gate_up(i)
     k1.record()
     torch.cuda.synchronize()
-    k_ms = k0.elapsed_time(k1) / k_iters
+    k_ms = max(k0.elapsed_time(k1) / k_iters, 1e-6)
     if prefill:
         k_flops = 2 * wl.T * wl.top_k * 2 * ip * wl.H
         achieved = k_flops / (k_ms * 1e-3) / 1e12
@@ -510,9 +530,19 @@ def main():
                     "frac": achieved / peaks["hbm_gbs"], "traffic": recorded_traffic(wl.name)}
     roofline.update({"kernel": "grouped_gemm_kernel<1> (gate_up + SiLU*mul)", "us_per_launch": k_ms * 1e3,
                      "peak_source": f"of {peaks['source']}", "launches_timed": k_iters})
+    if args.fp8:
+        # the fp8 kernels have no stand-alone entry point: the whole block against the HBM stream of its fp8 bytes
+        f8_bytes = (n_active * 3 * wl.H * wl.I * (1 + 4 / 16384) + wl.T * wl.H * (2 + 1 + 2)
+                    + wl.T * wl.top_k * (wl.I * (2 + 2 + 1 + 1) + wl.H * 4))
+        achieved = f8_bytes / (ms_per_step * 1e-3) / 1e9
+        roofline = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                    "frac": achieved / peaks["hbm_gbs"], "traffic": None,
+                    "kernel": "whole fp8 block (quantise x, permute, gate_up, quantise h, down, k-slot sum)",
+                    "us_per_launch": ms_per_step * 1e3, "peak_source": f"of {peaks['source']}", "launches_timed": steps,
+                    "algorithmic_bytes": f8_bytes}
 
     # whole-block fractions of both rooflines, for the record
-    blk_bytes = wl.algorithmic_bytes(n_active, tp)
+    blk_bytes = roofline["algorithmic_bytes"] if args.fp8 else wl.algorithmic_bytes(n_active, tp)
     block_stats = {"hbm_gbs": blk_bytes / (ms_per_step * 1e-3) / 1e9,
              "hbm_frac_of_measured": blk_bytes / (ms_per_step * 1e-3) / 1e9 / peaks["hbm_gbs"],
              "tflops_per_gpu": value / tp, "tensor_frac_of_measured_sustained": value / tp / peaks["bf16_tflops_sustained"],
@@ -520,7 +550,7 @@ def main():
 
     extras = {}
     # ---- config 2's comparison: the same tokens as 16 sequential chunks of 512 (what chunked prefill does)
-    if prefill and not mixed and wl.T % 512 == 0 and wl.T >= 1024:
+    if prefill and not mixed and not args.fp8 and wl.T % 512 == 0 and wl.T >= 1024:
         n_chunks = wl.T // 512
         xs = [x[c * 512:(c + 1) * 512].contiguous() for c in range(n_chunks)]
         ls = [logits[c * 512:(c + 1) * 512].contiguous() for c in range(n_chunks)]
@@ -583,11 +613,12 @@ def main():
         line = {
             "metric": "moe_block_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": steps,
             "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": wl.name, "T": wl.T, "H": wl.H, "E": wl.E, "top_k": wl.top_k, "I": wl.I,
+            "vs_baseline": None, "dtype": "fp8_e4m3 (w8a8, block scales, fp32 accumulation)" if args.fp8 else "bf16",
+            "data": "synthetic",
+            "config": {"workload": wl.name + ("-fp8" if args.fp8 else ""), "T": wl.T, "H": wl.H, "E": wl.E, "top_k": wl.top_k, "I": wl.I,
                        "tensor_parallel": tp, "I_per_rank": ip,
                        "launch": "cuda graph replay per step" if use_graph else "eager launches",
-                       "l2": f"weights rotate over {n_sets} distinct copies ({n_sets * 3 * wl.E * wl.H * ip * 2 / 1e6:.0f} MB per rank) so no step finds them in L2",
+                       "l2": f"weights rotate over {n_sets} distinct copies ({n_sets * 3 * wl.E * wl.H * ip * (1 if args.fp8 else 2) / 1e6:.0f} MB per rank) so no step finds them in L2",
                        "all_reduce": "fused k-slot sum + peer-memory all-reduce" if world > 1 else "none (1 GPU)"},
             "us_per_layer": ms_per_step * 1e3, "tokens_per_s": wl.T / (ms_per_step * 1e-3),
             "roofline": roofline, "block": block_stats, "cpu_baseline": cpu_baseline, "e2e": e2e,

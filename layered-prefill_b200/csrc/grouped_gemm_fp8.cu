@@ -212,12 +212,21 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_b, const Params
 #pragma unroll
       for (int i = 0; i < 64; ++i) acc[i] = 0.f;
 
+      // scales of the next K block are fetched while this one is processed (an L2 round trip is about as long
+      // as a whole K block at streaming rate)
+      float sa_n = valid ? a_s_row[0] : 0.f;
+      float w0_n = __ldg(w_s0);
+      float w1_n = kMode == 1 ? __ldg(w_s1) : 0.f;
       for (int kb = 0; kb < num_kb; ++kb, ++j) {
         const uint32_t b = j & 1u;
         const uint32_t bph = (j >> 1) & 1u;
-        const float sa = valid ? a_s_row[kb] : 0.f;
-        const float s0 = sa * __ldg(w_s0 + kb);
-        const float s1 = kMode == 1 ? sa * __ldg(w_s1 + kb) : s0;
+        const float s0 = sa_n * w0_n;
+        const float s1 = kMode == 1 ? sa_n * w1_n : s0;
+        if (kb + 1 < num_kb) {
+          sa_n = valid ? a_s_row[kb + 1] : 0.f;
+          w0_n = __ldg(w_s0 + kb + 1);
+          if (kMode == 1) w1_n = __ldg(w_s1 + kb + 1);
+        }
         ok = mbar_wait(&bar_part_full[b], bph);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) {
@@ -338,8 +347,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_b, const Params
 // One warp per (row, group of 128 columns): 4 values per lane.
 __global__ void __launch_bounds__(256)
 quant_rows_fp8_kernel(const __nv_bfloat16* __restrict__ x, int rows, int cols, uint8_t* __restrict__ q,
-                      float* __restrict__ s, const int* __restrict__ sorted_ids, int numel,
-                      const int* __restrict__ num_post_pad) {
+                      float* __restrict__ s) {
   grid_dependency_launch();
   grid_dependency_wait();
   const int groups = cols / kGroup;
@@ -348,7 +356,6 @@ quant_rows_fp8_kernel(const __nv_bfloat16* __restrict__ x, int rows, int cols, u
   if (w >= static_cast<long long>(rows) * groups) return;
   const int row = static_cast<int>(w / groups);
   const int g = static_cast<int>(w % groups);
-  if (sorted_ids != nullptr && (row >= *num_post_pad || sorted_ids[row] >= numel)) return;  // padding row
   const __nv_bfloat16* src = x + static_cast<long long>(row) * cols + g * kGroup + lane * 4;
   const uint2 raw = *reinterpret_cast<const uint2*>(src);
   const __nv_bfloat162 p0 = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
@@ -364,6 +371,41 @@ quant_rows_fp8_kernel(const __nv_bfloat16* __restrict__ x, int rows, int cols, u
     packed |= static_cast<uint32_t>(__nv_cvt_float_to_fp8(v[i] / scale, __NV_SATFINITE, __NV_E4M3)) << (8 * i);
   *reinterpret_cast<uint32_t*>(q + static_cast<long long>(row) * cols + g * kGroup + lane * 4) = packed;
   if (lane == 0) s[static_cast<long long>(row) * groups + g] = scale;
+}
+
+// Same quantisation for the permuted intermediate: one CTA per 128-row block of the permutation. A block's
+// valid rows come first (the permutation pads each expert at the end), so the CTA counts them once and its warps
+// walk (valid row, group) pairs only; decode batches have ~4 valid rows in a block of 128.
+__global__ void __launch_bounds__(256)
+quant_permuted_rows_fp8_kernel(const __nv_bfloat16* __restrict__ x, int cols, uint8_t* __restrict__ q,
+                               float* __restrict__ s, const int* __restrict__ sorted_ids, int numel,
+                               const int* __restrict__ num_post_pad) {
+  grid_dependency_launch();
+  grid_dependency_wait();
+  const int blk = blockIdx.x;
+  if (blk * BM >= *num_post_pad) return;
+  const int n_valid = __syncthreads_count(threadIdx.x < BM && sorted_ids[blk * BM + threadIdx.x] < numel);
+  const int groups = cols / kGroup;
+  const int lane = threadIdx.x & 31;
+  // gridDim.y CTAs share a block's tasks (prefill-sized batches: up to 128 valid rows per block)
+  for (int task = (threadIdx.x >> 5) + 8 * blockIdx.y; task < n_valid * groups; task += 8 * gridDim.y) {
+    const long long row = static_cast<long long>(blk) * BM + task / groups;
+    const int g = task % groups;
+    const uint2 raw = *reinterpret_cast<const uint2*>(x + row * cols + g * kGroup + lane * 4);
+    const __nv_bfloat162 p0 = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
+    const __nv_bfloat162 p1 = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+    const float v[4] = {__low2float(p0), __high2float(p0), __low2float(p1), __high2float(p1)};
+    float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, d));
+    const float scale = fmaxf(amax, 1e-10f) / 448.0f;
+    uint32_t packed = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      packed |= static_cast<uint32_t>(__nv_cvt_float_to_fp8(v[i] / scale, __NV_SATFINITE, __NV_E4M3)) << (8 * i);
+    *reinterpret_cast<uint32_t*>(q + row * cols + g * kGroup + lane * 4) = packed;
+    if (lane == 0) s[row * groups + g] = scale;
+  }
 }
 
 template <int kMode>
@@ -393,10 +435,18 @@ int launch_quant_rows_fp8(const __nv_bfloat16* x, int rows, int cols, uint8_t* q
   if (rows < 0 || cols <= 0 || cols % kGroup != 0)
     return set_error(kStatusInvalidArgument, "fp8 quantisation: the row length must be a multiple of %d (got %d)", kGroup, cols);
   if (rows == 0) return kStatusOk;
+  if (sorted_ids != nullptr) {
+    if (rows % BM != 0) return set_error(kStatusInvalidArgument, "fp8 quantisation of permuted rows: %d rows is not a multiple of %d", rows, BM);
+    if (int st = check_cuda(launch_pdl(quant_permuted_rows_fp8_kernel, dim3(static_cast<unsigned>(rows / BM), numel > 4096 ? 8u : 1u), dim3(256), 0,
+                                       stream, x, cols, q, s, sorted_ids, numel, num_post_pad),
+                            "quant_permuted_rows_fp8 launch"))
+      return st;
+    count_launches(1);
+    return check_launch("quant_permuted_rows_fp8");
+  }
   const long long warps = static_cast<long long>(rows) * (cols / kGroup);
   const unsigned blocks = static_cast<unsigned>((warps + 7) / 8);
-  if (int st = check_cuda(launch_pdl(quant_rows_fp8_kernel, dim3(blocks), dim3(256), 0, stream, x, rows, cols, q, s,
-                                     sorted_ids, numel, num_post_pad),
+  if (int st = check_cuda(launch_pdl(quant_rows_fp8_kernel, dim3(blocks), dim3(256), 0, stream, x, rows, cols, q, s),
                           "quant_rows_fp8 launch"))
     return st;
   count_launches(1);

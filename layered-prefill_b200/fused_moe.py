@@ -133,7 +133,7 @@ def fused_experts_impl(hidden_states: torch.Tensor, w1: torch.Tensor, w2: torch.
 
 def _fused_experts_fp8(hidden_states, w1, w2, topk_weights, topk_ids, inplace, activation, w1_scale, w2_scale,
                        block_shape, w1_bias, w2_bias, a1_scale, a2_scale, w1_zp, w2_zp, expert_map,
-                       apply_router_weight_on_input) -> torch.Tensor:
+                       apply_router_weight_on_input, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """w8a8 e4m3: weights [E, 2I, H] / [E, H, I] with fp32 scales per 128 x 128 block, activations quantised per
     token and 128 columns inside the library (dynamic, so a1_scale / a2_scale stay None)."""
     if not hidden_states.is_cuda:
@@ -162,7 +162,9 @@ def _fused_experts_fp8(hidden_states, w1, w2, topk_weights, topk_ids, inplace, a
     assert s1.shape == (E, 2 * inter // 128, H // 128), f"w1_scale shape {tuple(s1.shape)}"
     assert s2.shape == (E, H // 128, inter // 128), f"w2_scale shape {tuple(s2.shape)}"
     k = topk_ids.size(1)
-    out = hidden_states if inplace else torch.empty_like(hidden_states)
+    if out is None:
+        out = hidden_states if inplace else torch.empty_like(hidden_states)
+    assert out.shape == hidden_states.shape and out.dtype == torch.bfloat16 and out.is_contiguous()
     if T == 0:
         return out
     tw = topk_weights.to(torch.float32).contiguous()
@@ -178,6 +180,15 @@ def _fused_experts_fp8(hidden_states, w1, w2, topk_weights, topk_ids, inplace, a
             ctypes.cast(s2.data_ptr(), fptr), tw.data_ptr(), ti.data_ptr(), out.data_ptr(), T, E, k, H, inter,
             ws.data_ptr(), ws.numel(), ops.status_word(dev).data_ptr(), torch.cuda.current_stream().cuda_stream))
     return out
+
+
+def fused_moe_forward_fp8(hidden_states: torch.Tensor, router_logits: torch.Tensor, w13_q: torch.Tensor,
+                          w13_scale: torch.Tensor, w2_q: torch.Tensor, w2_scale: torch.Tensor, top_k: int,
+                          renormalize: bool = True, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Router + fp8 experts: what FusedMoE.forward does (layers/fused_moe.py:590-612) with e4m3 block-scaled weights."""
+    tw, ti, _ = fused_topk(hidden_states, router_logits, top_k, renormalize)
+    return _fused_experts_fp8(hidden_states, w13_q, w2_q, tw, ti, False, "silu", w13_scale, w2_scale, [128, 128], None,
+                              None, None, None, None, None, None, False, out=out)
 
 
 def per_token_group_quant_fp8(x: torch.Tensor, group_size: int = 128):

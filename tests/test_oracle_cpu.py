@@ -151,3 +151,49 @@ def test_all_reduce_order_and_single_rounding():
     # fp32 accumulation keeps the two small addends, a per-step bf16 rounding would lose them
     assert out[0].item() == torch.tensor(1.0 + 2.0 ** -8).to(torch.bfloat16).item()
     assert out[1].item() == 258.0
+
+
+# ---------------------------------------------------------------- fp8 emulation (no reference counterpart: parity unpinned)
+def test_fp8_activation_quantisation_properties():
+    g = torch.Generator().manual_seed(0)
+    x = (torch.randn(9, 384, generator=g) * 2).to(torch.bfloat16)
+    x[0, :128] = 0
+    q, s = O.per_token_group_quant_fp8(x)
+    assert q.dtype == torch.float8_e4m3fn and s.shape == (9, 3)
+    assert s[0, 0].item() == pytest.approx(1e-10 / 448.0)
+    assert torch.all(q[0, :128].float() == 0)
+    # every group uses the whole e4m3 range: its largest magnitude maps to +-448
+    assert torch.all(q.float().view(9, 3, 128).abs().amax(-1)[1:] == 448.0)
+    deq = q.float().view(9, 3, 128) * s[..., None]
+    err = (deq - x.float().view(9, 3, 128)).abs()
+    # e4m3 has 3 mantissa bits: relative error <= 2^-4 for normal values, absolute <= scale * 2^-10 for subnormals
+    assert torch.all(err <= x.float().view(9, 3, 128).abs() * 2 ** -4 + s[..., None] * 2 ** -9)
+
+
+def test_fp8_weight_block_quantisation_round_trip():
+    g = torch.Generator().manual_seed(1)
+    w = (torch.randn(3, 192, 256, generator=g) * 0.02).to(torch.bfloat16)   # 192 rows: a ragged last scale block
+    q, s = O.quant_weight_block_fp8(w)
+    assert q.shape == w.shape and s.shape == (3, 2, 2)
+    deq = O.dequant_weight_block_fp8(q, s)
+    assert O.rel_l2(deq, w) <= 4e-2
+    # given scales (the benchmark config's recipe) are used as they are
+    sc = torch.full((3, 2, 2), 1.0 / 448)
+    q2, s2 = O.quant_weight_block_fp8(w, sc)
+    assert torch.equal(s2, sc)
+    assert O.rel_l2(O.dequant_weight_block_fp8(q2, s2), w) <= 6e-2
+
+
+def test_fp8_experts_emulation_tracks_bf16_math_on_dequantised_weights():
+    g = torch.Generator().manual_seed(2)
+    T, H, E, k, I = 48, 256, 4, 2, 128
+    x = torch.randn(T, H, generator=g).to(torch.bfloat16)
+    w13 = (torch.randn(E, 2 * I, H, generator=g) * 0.05).to(torch.bfloat16)
+    w2 = (torch.randn(E, H, I, generator=g) * 0.05).to(torch.bfloat16)
+    q13, s13 = O.quant_weight_block_fp8(w13)
+    q2, s2 = O.quant_weight_block_fp8(w2)
+    tw, ti, _ = O.fused_topk(x, torch.randn(T, E, generator=g), k, True)
+    got = O.fused_experts_fp8(x, q13, s13, q2, s2, tw, ti)
+    want = O.fused_experts(x, O.dequant_weight_block_fp8(q13, s13).to(torch.bfloat16),
+                           O.dequant_weight_block_fp8(q2, s2).to(torch.bfloat16), tw, ti, "silu", "exact")
+    assert O.rel_l2(got, want) <= 8e-2
