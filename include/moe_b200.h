@@ -44,6 +44,33 @@ int moe_b200_block_m(void);
 uint64_t moe_b200_launch_count(void);
 
 /*
+ * RMSNorm with the reference's rounding and summation order (bit-identical for H % 32 == 0). Replace
+ * ops.rms_norm / ops.add_rms_norm (csrc/ops.cpp:16-27, csrc/layernorm_kernels.cu:10-36, 76-107).
+ *   add_rms_norm: residual <- bf16(input + residual); out <- bf16(bf16(residual * rsqrt(mean(residual^2) + eps)) * weight)
+ * bf16 [T, H] contiguous, weight bf16 [H]; H % 8 == 0, H <= 24000.
+ */
+int moe_b200_rms_norm(void* out, const void* input, const void* weight, float eps, int T, int H, void* stream);
+int moe_b200_add_rms_norm(void* out, void* residual, const void* input, const void* weight, float eps, int T, int H,
+                          void* stream);
+
+/*
+ * The decoder layer's three steps in front of the MoE block in one call: post-attention add + RMSNorm, the router's
+ * gate projection and softmax/top-k. Replaces the sequence post_attention_layernorm -> gate -> select_experts
+ * (nanovllm/models/qwen3_moe.py:276-282 and :100-110, nanovllm/layers/fused_moe.py:712-724).
+ *   input bf16 [T, H] (attention output), residual bf16 [T, H] (updated in place), norm_weight bf16 [H],
+ *   gate_weight bf16 [E, H] (ReplicatedLinear.weight), normed_out bf16 [T, H] (the MoE block's hidden states),
+ *   logits_out bf16 [T, E] or NULL, topk_weights fp32 [T, k], topk_ids int32 [T, k].
+ * One kernel for T <= 512 with E in {128, 256} and H % 256 == 0; otherwise norm, tensor-core GEMM and routing as
+ * separate launches (needs the workspace; E % 16 == 0, H % 16 == 0). Logits are the bf16 rounding of an fp32
+ * dot product whose summation order differs from the reference's cuBLAS call.
+ */
+size_t moe_b200_pre_moe_workspace_bytes(int T, int H, int E);
+int moe_b200_add_rms_norm_router(const void* input, void* residual, const void* norm_weight, float eps,
+                                 const void* gate_weight, void* normed_out, void* logits_out, float* topk_weights,
+                                 int32_t* topk_ids, int T, int H, int E, int top_k, int renormalize, void* workspace,
+                                 size_t workspace_bytes, int32_t* status_word, void* stream);
+
+/*
  * Router. Replaces ops.topk_softmax (csrc/ops.cpp:46-51, csrc/moe_topk_softmax_kernels.cu:476-503)
  * and, with renormalize != 0, the division in fused_topk (nanovllm/layers/for_moe/fused_moe.py:417-418).
  * gating: [T, E] row-major, fp32 (gating_is_bf16 == 0) or bf16 (!= 0). Outputs [T, k]:

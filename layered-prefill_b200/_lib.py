@@ -51,6 +51,10 @@ SIGNATURES = {
     "moe_b200_launch_count": (ctypes.c_uint64, []),
     "moe_b200_grouped_gemm_gate_up": (c_int, [c_void_p] * 7 + [c_int] * 7 + [c_void_p, c_void_p]),
     "moe_b200_grouped_gemm_down": (c_int, [c_void_p, c_int] + [c_void_p] * 7 + [c_int] * 5 + [c_void_p, c_void_p]),
+    "moe_b200_rms_norm": (c_int, [c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_void_p]),
+    "moe_b200_add_rms_norm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_void_p]),
+    "moe_b200_pre_moe_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
+    "moe_b200_add_rms_norm_router": (c_int, [c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p] + [c_int] * 5 + [c_void_p, c_size_t, c_void_p, c_void_p]),
     "moe_b200_topk_softmax": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
     "moe_b200_align_workspace_bytes": (c_size_t, [c_int, c_int]),
     "moe_b200_moe_align_block_size": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_size_t, c_void_p]),

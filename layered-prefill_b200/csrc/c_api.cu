@@ -303,6 +303,40 @@ int moe_b200_fused_experts(const void* x, const void* w13, const void* w2, const
                         H, s);
 }
 
+int moe_b200_rms_norm(void* out, const void* input, const void* weight, float eps, int T, int H, void* stream) {
+  if (out == nullptr || input == nullptr || weight == nullptr) return set_error(kStatusInvalidArgument, "rms_norm: null pointer");
+  return launch_rms_norm(static_cast<__nv_bfloat16*>(out), nullptr, static_cast<const __nv_bfloat16*>(input),
+                         static_cast<const __nv_bfloat16*>(weight), eps, T, H, static_cast<cudaStream_t>(stream));
+}
+
+int moe_b200_add_rms_norm(void* out, void* residual, const void* input, const void* weight, float eps, int T, int H,
+                          void* stream) {
+  if (out == nullptr || residual == nullptr || input == nullptr || weight == nullptr)
+    return set_error(kStatusInvalidArgument, "add_rms_norm: null pointer");
+  return launch_rms_norm(static_cast<__nv_bfloat16*>(out), static_cast<__nv_bfloat16*>(residual),
+                         static_cast<const __nv_bfloat16*>(input), static_cast<const __nv_bfloat16*>(weight), eps, T, H,
+                         static_cast<cudaStream_t>(stream));
+}
+
+size_t moe_b200_pre_moe_workspace_bytes(int T, int H, int E) {
+  if (T < 0 || H <= 0 || E <= 0) return 0;
+  return pre_moe_workspace_bytes(T, H, E);
+}
+
+int moe_b200_add_rms_norm_router(const void* input, void* residual, const void* norm_weight, float eps,
+                                 const void* gate_weight, void* normed_out, void* logits_out, float* topk_weights,
+                                 int32_t* topk_ids, int T, int H, int E, int top_k, int renormalize, void* workspace,
+                                 size_t workspace_bytes, int32_t* status_word, void* stream) {
+  if (input == nullptr || residual == nullptr || norm_weight == nullptr || gate_weight == nullptr || normed_out == nullptr ||
+      topk_weights == nullptr || topk_ids == nullptr || status_word == nullptr)
+    return set_error(kStatusInvalidArgument, "add_rms_norm_router: null pointer");
+  return launch_add_rms_norm_router(static_cast<const __nv_bfloat16*>(input), static_cast<__nv_bfloat16*>(residual),
+                                    static_cast<const __nv_bfloat16*>(norm_weight), eps,
+                                    static_cast<const __nv_bfloat16*>(gate_weight), static_cast<__nv_bfloat16*>(normed_out),
+                                    static_cast<__nv_bfloat16*>(logits_out), topk_weights, topk_ids, T, H, E, top_k,
+                                    renormalize, workspace, workspace_bytes, status_word, static_cast<cudaStream_t>(stream));
+}
+
 int moe_b200_quant_fp8_per_token_group(const void* x, int rows, int cols, void* q, float* scales, void* stream) {
   if (x == nullptr || q == nullptr || scales == nullptr) return set_error(kStatusInvalidArgument, "quant_fp8_per_token_group: null pointer");
   return launch_quant_rows_fp8(static_cast<const __nv_bfloat16*>(x), rows, cols, static_cast<uint8_t*>(q), scales, nullptr,

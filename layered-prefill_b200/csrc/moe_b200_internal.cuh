@@ -79,6 +79,16 @@ int launch_grouped_gemm2(const GroupedGemmArgs& a, const __nv_bfloat16* h_sorted
                          __nv_bfloat16* c3, cudaStream_t stream);
 int device_sm_count();
 
+// ---- pre_moe.cu (the decoder layer's steps in front of the MoE block)
+// residual != nullptr: residual <- bf16(input + residual) first (ops.add_rms_norm); else ops.rms_norm.
+int launch_rms_norm(__nv_bfloat16* out, __nv_bfloat16* residual, const __nv_bfloat16* input, const __nv_bfloat16* weight,
+                    float eps, int T, int H, cudaStream_t stream);
+size_t pre_moe_workspace_bytes(int T, int H, int E);
+int launch_add_rms_norm_router(const __nv_bfloat16* input, __nv_bfloat16* residual, const __nv_bfloat16* norm_weight, float eps,
+                               const __nv_bfloat16* gate_weight, __nv_bfloat16* normed, __nv_bfloat16* logits_out,
+                               float* topk_w, int* topk_ids, int T, int H, int E, int top_k, int renormalize,
+                               void* workspace, size_t workspace_bytes, int* status_word, cudaStream_t stream);
+
 // ---- grouped_gemm_fp8.cu (e4m3 weights with 128 x 128 block scales, activations quantised per row and 128 columns)
 // q[r, c] = e4m3(x[r, c] / s[r, c / 128]), s = max(|x| over the group, 1e-10) / 448. With sorted_ids given, rows that are
 // padding of the permutation (or lie beyond *num_post_pad) are skipped.

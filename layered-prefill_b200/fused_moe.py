@@ -182,6 +182,38 @@ def _fused_experts_fp8(hidden_states, w1, w2, topk_weights, topk_ids, inplace, a
     return out
 
 
+def pre_moe(hidden_states: torch.Tensor, residual: torch.Tensor, norm_weight: torch.Tensor, eps: float,
+            gate_weight: torch.Tensor, top_k: int, renormalize: bool = True, return_logits: bool = False):
+    """The decoder layer's steps in front of the MoE block (nanovllm/models/qwen3_moe.py:276-282 and :100-110):
+    post_attention_layernorm(hidden_states, residual) -> gate -> softmax/top-k, one library call.
+
+    hidden_states: bf16 [T, H] attention output (not modified); residual: bf16 [T, H], updated in place;
+    norm_weight: RMSNorm.weight [H]; gate_weight: ReplicatedLinear.weight [E, H].
+    Returns (normed hidden states, residual, topk_weights fp32 [T, k], topk_ids int32 [T, k][, router_logits bf16 [T, E]])."""
+    if not hidden_states.is_cuda:
+        raise RuntimeError("pre_moe needs CUDA tensors; there is no CPU path")
+    for t in (hidden_states, residual, norm_weight, gate_weight):
+        assert t.dtype == torch.bfloat16 and t.is_contiguous()
+    T, H = hidden_states.shape
+    E = gate_weight.size(0)
+    assert residual.shape == (T, H) and norm_weight.numel() == H and gate_weight.shape == (E, H)
+    dev = hidden_states.device
+    normed = torch.empty_like(hidden_states)
+    tw = torch.empty(T, top_k, dtype=torch.float32, device=dev)
+    ti = torch.empty(T, top_k, dtype=torch.int32, device=dev)
+    logits = torch.empty(T, E, dtype=torch.bfloat16, device=dev) if return_logits else None
+    if T > 0:
+        nbytes = lib.moe_b200_pre_moe_workspace_bytes(T, H, E)
+        ws = _workspaces.get(dev, nbytes)
+        with torch.cuda.device(dev):
+            check(lib.moe_b200_add_rms_norm_router(
+                hidden_states.data_ptr(), residual.data_ptr(), norm_weight.data_ptr(), float(eps), gate_weight.data_ptr(),
+                normed.data_ptr(), logits.data_ptr() if logits is not None else 0, tw.data_ptr(), ti.data_ptr(), T, H, E,
+                top_k, 1 if renormalize else 0, ws.data_ptr(), ws.numel(), ops.status_word(dev).data_ptr(),
+                torch.cuda.current_stream().cuda_stream))
+    return (normed, residual, tw, ti, logits) if return_logits else (normed, residual, tw, ti)
+
+
 def fused_moe_forward_fp8(hidden_states: torch.Tensor, router_logits: torch.Tensor, w13_q: torch.Tensor,
                           w13_scale: torch.Tensor, w2_q: torch.Tensor, w2_scale: torch.Tensor, top_k: int,
                           renormalize: bool = True, out: Optional[torch.Tensor] = None) -> torch.Tensor:

@@ -44,6 +44,34 @@ def read_status(device: torch.device | None = None) -> int:
     return int(v.value)
 
 
+def _norm_args(out: torch.Tensor, input: torch.Tensor, weight: torch.Tensor):  # noqa: A002
+    _need_cuda(out, input, weight)
+    if input.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16:
+        raise RuntimeError("rms_norm: bfloat16 tensors only")
+    assert input.is_contiguous() and out.is_contiguous() and weight.is_contiguous() and out.shape == input.shape
+    H = input.size(-1)
+    assert weight.numel() == H
+    return (input.numel() // H if H else 0), H
+
+
+def rms_norm(out: torch.Tensor, input: torch.Tensor, weight: torch.Tensor, epsilon: float) -> None:  # noqa: A002
+    """csrc/ops.cpp:16-21. out = bf16(bf16(x * rsqrt(mean(x^2) + eps)) * weight); out may be input."""
+    T, H = _norm_args(out, input, weight)
+    with torch.cuda.device(input.device):
+        check(lib.moe_b200_rms_norm(out.data_ptr(), input.data_ptr(), weight.data_ptr(), float(epsilon), T, H, _stream()))
+
+
+def add_rms_norm(out: torch.Tensor, residual: torch.Tensor, input: torch.Tensor, weight: torch.Tensor,  # noqa: A002
+                 epsilon: float) -> None:
+    """csrc/ops.cpp:22-27. residual <- bf16(input + residual) in place, out = its RMS norm times weight."""
+    T, H = _norm_args(out, input, weight)
+    _need_cuda(residual)
+    assert residual.dtype == torch.bfloat16 and residual.is_contiguous() and residual.shape == input.shape
+    with torch.cuda.device(input.device):
+        check(lib.moe_b200_add_rms_norm(out.data_ptr(), residual.data_ptr(), input.data_ptr(), weight.data_ptr(),
+                                        float(epsilon), T, H, _stream()))
+
+
 def topk_softmax(topk_weights: torch.Tensor, topk_indices: torch.Tensor, token_expert_indices: torch.Tensor,
                  gating_output: torch.Tensor) -> None:
     """csrc/ops.cpp:46-51. gating_output fp32 (or bf16) [T, E]; outputs [T, k]."""
