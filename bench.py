@@ -578,6 +578,54 @@ def main():
             "speedup_single_pass": c_ms / ms_per_step,
             "weight_bytes_chunked": sum(act_chunks) * per_expert, "weight_bytes_single_pass": n_active * per_expert,
             "expert_reload_bytes_saved": (sum(act_chunks) - n_active) * per_expert}
+    # ---- the steps in front of the block (add + RMSNorm, gate projection, top-k): one library call against the
+    # reference's sequence of three ops (its norm kernel's twin, a cuBLAS linear, the routing kernel)
+    if not mixed and not args.fp8 and world == 1:
+        import torch.nn.functional as F
+        gpre = torch.Generator(device=dev)
+        gpre.manual_seed(7)
+        attn = torch.randn(wl.T, wl.H, generator=gpre, device=dev).to(torch.bfloat16)
+        resid = torch.randn(wl.T, wl.H, generator=gpre, device=dev).to(torch.bfloat16)
+        nw = torch.ones(wl.H, device=dev, dtype=torch.bfloat16)
+        wg = (torch.randn(wl.E, wl.H, generator=gpre, device=dev) * 0.02).to(torch.bfloat16)
+        normed_buf = torch.empty_like(attn)
+
+        def fused_pre(i):
+            fused_moe.pre_moe(attn, resid, nw, 1e-6, wg, wl.top_k, True)
+
+        def three_ops(i):
+            ops.add_rms_norm(normed_buf, resid, attn, nw, 1e-6)
+            fused_moe.fused_topk(normed_buf, F.linear(normed_buf, wg), wl.top_k, True)
+
+        pre = {}
+        for label, fn in (("one_call_us", fused_pre), ("three_ops_us", three_ops)):
+            for i in range(5):
+                fn(i)
+            torch.cuda.synchronize()
+            run = fn
+            if not prefill:  # device time, not Python call overhead: replay a captured graph
+                side2 = torch.cuda.Stream(device=dev)
+                side2.wait_stream(torch.cuda.current_stream())
+                gq = torch.cuda.CUDAGraph()
+                with torch.cuda.stream(side2):
+                    fn(0)
+                    with torch.cuda.graph(gq, stream=side2):
+                        fn(0)
+                torch.cuda.current_stream().wait_stream(side2)
+                run = lambda i, gq=gq: gq.replay()  # noqa: E731
+                run(0)
+                torch.cuda.synchronize()
+            p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            reps = 50 if prefill else 300
+            p0.record()
+            for i in range(reps):
+                run(i)
+            p1.record()
+            torch.cuda.synchronize()
+            pre[label] = p0.elapsed_time(p1) / reps * 1e3
+        pre["note"] = ("graph replay" if not prefill else "eager launches") + \
+            "; inputs L2-resident across repetitions; three_ops = add_rms_norm + torch linear (cuBLAS) + routing kernel"
+        extras["pre_moe"] = pre
     # ---- all-reduce alone (N > 1): the [T, H] bf16 reduction of this workload's batch sizes
     if world > 1:
         ar = {}

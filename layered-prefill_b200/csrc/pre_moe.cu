@@ -3,9 +3,9 @@
 //   hidden, residual = post_attention_layernorm(hidden, residual)     ops.add_rms_norm, csrc/layernorm_kernels.cu:76-107
 //   router_logits    = gate(hidden)                                   bf16 linear [T,H] x [E,H]^T, layers/linear.py:53-60
 //   topk_weights/ids = softmax + top-k (+ renormalise)                the routing kernel of this library
-// For decode-sized batches one kernel does all three per token row (one CTA per row): the normalised row
-// stays in shared memory, eight warps form the E dot products with the lanes striding along H, one warp picks
-// the experts. For large batches the same results come from three launches: the norm kernel, the tensor-core
+// For decode-sized batches one kernel does all three per token row (a cluster of eight CTAs per row): the
+// normalised row stays in shared memory, each CTA forms an eighth of the E dot products with the lanes striding
+// along H and hands them to the first CTA through distributed shared memory, whose first warp picks the experts. For large batches the same results come from three launches: the norm kernel, the tensor-core
 // grouped GEMM of this library run as a plain GEMM (one "expert" = the gate weight, identity permutation), and
 // the routing kernel.
 //
@@ -18,6 +18,7 @@
 
 #include "launch.cuh"
 #include "moe_b200_internal.cuh"
+#include "ptx.cuh"
 #include "routing_core.cuh"
 
 namespace moe_b200 {
@@ -62,11 +63,14 @@ __device__ __forceinline__ float reference_block_sum(const float (&p_in)[8], int
 }
 
 // residual <- bf16(input + residual) (or stays input when kAdd is false), out <- bf16(bf16(r * rsqrt(mean(r^2) + eps)) * w).
-// When x_row is given the normalised row is also left there (shared memory of the fused kernel).
-template <bool kAdd, int kCtaThreads>
+// The normalised row is also left in x_row (shared memory). Nothing is written to global memory before every
+// thread has read its inputs; with kClusterSync that holds across the CTAs of a cluster working on the same row
+// (each forms the row for itself, `write_global` picks the one that stores it).
+template <bool kAdd, int kCtaThreads, bool kClusterSync>
 __device__ __forceinline__ void rms_norm_row(const __nv_bfloat16* in_row, __nv_bfloat16* res_row,
                                              const __nv_bfloat16* __restrict__ weight, __nv_bfloat16* out_row,
-                                             int H, float eps, __nv_bfloat16* x_row, float* red, float* total_slot) {
+                                             int H, float eps, __nv_bfloat16* x_row, float* red, float* total_slot,
+                                             bool write_global) {
   const int t = threadIdx.x;
   float p[8];
 #pragma unroll
@@ -82,22 +86,23 @@ __device__ __forceinline__ void rms_norm_row(const __nv_bfloat16* in_row, __nv_b
         p[i] = fmaf(x, x, p[i]);
         a.h[i] = __float2bfloat16_rn(x);  // what the second pass of the reference reads back
       }
-      if (kAdd) *reinterpret_cast<uint4*>(res_row + c) = a.u;
       *reinterpret_cast<uint4*>(x_row + c) = a.u;
     }
   }
   const float total = reference_block_sum<kCtaThreads>(p, t, red, total_slot);
+  if (kClusterSync) cluster_sync_all();
   const float s = rsqrtf(total / H + eps);
   for (int c = 8 * t; c < H; c += 8 * kCtaThreads) {
     Bf16x8 xv, wv;
     xv.u = *reinterpret_cast<const uint4*>(x_row + c);
     wv.u = *reinterpret_cast<const uint4*>(weight + c);
+    if (kAdd && write_global) *reinterpret_cast<uint4*>(res_row + c) = xv.u;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       const __nv_bfloat16 scaled = __float2bfloat16_rn(__bfloat162float(xv.h[i]) * s);
       xv.h[i] = __float2bfloat16_rn(__bfloat162float(scaled) * __bfloat162float(wv.h[i]));
     }
-    *reinterpret_cast<uint4*>(out_row + c) = xv.u;
+    if (write_global) *reinterpret_cast<uint4*>(out_row + c) = xv.u;
     *reinterpret_cast<uint4*>(x_row + c) = xv.u;
   }
 }
@@ -114,38 +119,46 @@ rms_norm_kernel(__nv_bfloat16* out, __nv_bfloat16* residual, const __nv_bfloat16
   if (threadIdx.x < 33) red[threadIdx.x] = 0.f;
   __syncthreads();
   const size_t off = static_cast<size_t>(blockIdx.x) * H;
-  rms_norm_row<kAdd, kNormThreads>(input + off, kAdd ? residual + off : nullptr, weight, out + off, H, eps, x_row, red,
-                                   red + 32);
+  rms_norm_row<kAdd, kNormThreads, false>(input + off, kAdd ? residual + off : nullptr, weight, out + off, H, eps, x_row,
+                                          red, red + 32, true);
 }
 
-constexpr int kFusedThreads = 256;
+// Decode-sized batches: a cluster of 8 CTAs per token row. Every CTA forms the normalised row in its own shared
+// memory (the row is 4 KB; re-reading the gate weight per row is what costs, so that is what is split), computes
+// E/8 of the gate logits with its four warps, and stores them into CTA 0's shared memory; after the cluster
+// barrier CTA 0's first warp runs the routing. (One CTA per row took 17 us at T=64: 512 KB of gate weight through
+// one SM; the reference's three launches take 12 us.)
+constexpr int kClusterCtas = 8;
+constexpr int kClusterThreads = 128;
 
 template <int E>
-__global__ void __launch_bounds__(kFusedThreads)
-pre_moe_fused_kernel(const __nv_bfloat16* __restrict__ input, __nv_bfloat16* __restrict__ residual,
-                     const __nv_bfloat16* __restrict__ norm_weight, float eps, const __nv_bfloat16* __restrict__ gate_weight,
-                     __nv_bfloat16* __restrict__ normed, __nv_bfloat16* __restrict__ logits_out, float* __restrict__ topk_w,
-                     int* __restrict__ topk_ids, int T, int H, int k, int renormalize) {
+__global__ void __launch_bounds__(kClusterThreads)
+pre_moe_cluster_kernel(const __nv_bfloat16* input, __nv_bfloat16* residual, const __nv_bfloat16* __restrict__ norm_weight,
+                       float eps, const __nv_bfloat16* __restrict__ gate_weight, __nv_bfloat16* normed,
+                       __nv_bfloat16* __restrict__ logits_out, float* __restrict__ topk_w, int* __restrict__ topk_ids, int T,
+                       int H, int k, int renormalize) {
   extern __shared__ uint4 fused_smem[];
   grid_dependency_launch();
   grid_dependency_wait();
   __nv_bfloat16* x_row = reinterpret_cast<__nv_bfloat16*>(fused_smem);
   float* red = reinterpret_cast<float*>(x_row + H);
   float* logit_s = red + 40;
-  if (threadIdx.x < 33) red[threadIdx.x] = 0.f;
-  __syncthreads();
-  const int row = blockIdx.x;
+  const uint32_t rank = cluster_ctarank();
+  const int row = blockIdx.x / kClusterCtas;
   const size_t off = static_cast<size_t>(row) * H;
-  rms_norm_row<true, kFusedThreads>(input + off, residual + off, norm_weight, normed + off, H, eps, x_row, red, red + 32);
+  rms_norm_row<true, kClusterThreads, true>(input + off, residual + off, norm_weight, normed + off, H, eps, x_row, red,
+                                            red + 32, rank == 0);
   __syncthreads();
 
-  // gate projection: warp w takes experts [w * E/8, (w+1) * E/8), four at a time; a lane covers 8 columns of every
+  // gate projection: this CTA's E/8 experts, E/32 per warp in groups of four; a lane covers 8 columns of every
   // 256-column slice of the row
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
-  constexpr int kPerWarp = E / 8;
+  constexpr int kPerCta = E / kClusterCtas;
+  constexpr int kPerWarp = kPerCta / 4;
   const int slices = H / 256;
-  for (int e0 = warp * kPerWarp; e0 < (warp + 1) * kPerWarp; e0 += 4) {
+  for (int e0 = static_cast<int>(rank) * kPerCta + warp * kPerWarp; e0 < static_cast<int>(rank) * kPerCta + (warp + 1) * kPerWarp;
+       e0 += 4) {
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
     for (int c = 0; c < slices; ++c) {
       Bf16x8 xv;
@@ -167,15 +180,15 @@ pre_moe_fused_kernel(const __nv_bfloat16* __restrict__ input, __nv_bfloat16* __r
     if (lane < 4) {
       const float mine = lane == 0 ? acc[0] : lane == 1 ? acc[1] : lane == 2 ? acc[2] : acc[3];
       const __nv_bfloat16 l = __float2bfloat16_rn(mine);  // the linear layer's bf16 output
-      logit_s[e0 + lane] = __bfloat162float(l);
+      st_cluster_f32(&logit_s[e0 + lane], 0, __bfloat162float(l));
       if (logits_out != nullptr) logits_out[static_cast<size_t>(row) * E + e0 + lane] = l;
     }
   }
-  __syncthreads();
+  cluster_sync_all();  // every CTA's logits have landed in CTA 0; nobody leaves before CTA 0 could be written
 
-  if (warp == 0) {
+  if (rank == 0 && warp == 0) {
     using S = TopkShape<E>;
-    static_assert(S::kThreadsPerRow == 32, "the fused kernel gives one warp to the row");
+    static_assert(S::kThreadsPerRow == 32, "one warp routes the row");
     float v[S::kVpt];
 #pragma unroll
     for (int ii = 0; ii < S::kVecsPerThread; ++ii)
@@ -256,14 +269,17 @@ int launch_add_rms_norm_router(const __nv_bfloat16* input, __nv_bfloat16* residu
   if (T == 0) return kStatusOk;
   if (fused_shape_ok(T, H, E)) {
     const size_t smem = static_cast<size_t>(H) * 2 + (40 + E) * sizeof(float);
+    const dim3 grid(static_cast<unsigned>(T) * kClusterCtas);
     const cudaError_t e =
-        E == 128 ? launch_pdl(pre_moe_fused_kernel<128>, dim3(T), dim3(kFusedThreads), smem, stream, input, residual, norm_weight,
-                              eps, gate_weight, normed, logits_out, topk_w, topk_ids, T, H, top_k, renormalize)
-                 : launch_pdl(pre_moe_fused_kernel<256>, dim3(T), dim3(kFusedThreads), smem, stream, input, residual, norm_weight,
-                              eps, gate_weight, normed, logits_out, topk_w, topk_ids, T, H, top_k, renormalize);
-    if (int st = check_cuda(e, "pre_moe_fused launch")) return st;
+        E == 128 ? launch_pdl_cluster(pre_moe_cluster_kernel<128>, grid, dim3(kClusterThreads), smem, stream, kClusterCtas, input,
+                                      residual, norm_weight, eps, gate_weight, normed, logits_out, topk_w, topk_ids, T, H,
+                                      top_k, renormalize)
+                 : launch_pdl_cluster(pre_moe_cluster_kernel<256>, grid, dim3(kClusterThreads), smem, stream, kClusterCtas, input,
+                                      residual, norm_weight, eps, gate_weight, normed, logits_out, topk_w, topk_ids, T, H,
+                                      top_k, renormalize);
+    if (int st = check_cuda(e, "pre_moe_cluster launch")) return st;
     count_launches(1);
-    return check_launch("pre_moe_fused");
+    return check_launch("pre_moe_cluster");
   }
   // large batches (or other expert counts): norm, tensor-core GEMM, routing as three launches
   if (E % 16 != 0) return set_error(kStatusInvalidArgument, "add_rms_norm_router: the expert count must be a multiple of 16 (got %d)", E);
