@@ -197,3 +197,31 @@ def test_fp8_experts_emulation_tracks_bf16_math_on_dequantised_weights():
     want = O.fused_experts(x, O.dequant_weight_block_fp8(q13, s13).to(torch.bfloat16),
                            O.dequant_weight_block_fp8(q2, s2).to(torch.bfloat16), tw, ti, "silu", "exact")
     assert O.rel_l2(got, want) <= 8e-2
+
+
+# ---------------------------------------------------------------- the steps in front of the block
+def test_add_rms_norm_oracle_rounding_points():
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(6, 256, generator=g).to(torch.bfloat16)
+    res = (torch.randn(6, 256, generator=g) * 3).to(torch.bfloat16)
+    w = (1 + 0.2 * torch.randn(256, generator=g)).to(torch.bfloat16)
+    out, r = O.add_rms_norm(x, res, w, 1e-6)
+    # the residual is the bf16 rounding of the fp32 sum; the variance uses the unrounded sum
+    s32 = x.float() + res.float()
+    assert torch.equal(r, s32.to(torch.bfloat16))
+    scale = torch.rsqrt((s32.double() ** 2).mean(-1, keepdim=True) + 1e-6).float()
+    want = ((r.float() * scale).to(torch.bfloat16).float() * w.float()).to(torch.bfloat16)
+    assert ((out.float() - want.float()).abs() <= want.float().abs() * 2 ** -7 + 1e-6).all()
+    # without a residual the input itself is normalised
+    out2, r2 = O.add_rms_norm(x, None, w, 1e-6)
+    assert torch.equal(r2, x)
+    assert out2.shape == x.shape and out2.dtype == torch.bfloat16
+
+
+def test_router_gate_oracle_is_a_bf16_linear():
+    g = torch.Generator().manual_seed(6)
+    h = torch.randn(5, 128, generator=g).to(torch.bfloat16)
+    wg = (torch.randn(16, 128, generator=g) * 0.02).to(torch.bfloat16)
+    lg = O.router_gate(h, wg)
+    assert lg.dtype == torch.bfloat16 and lg.shape == (5, 16)
+    assert torch.equal(lg, torch.nn.functional.linear(h.float(), wg.float()).to(torch.bfloat16))
