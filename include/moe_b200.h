@@ -274,6 +274,35 @@ int moe_b200_fused_moe_forward_tp(const void* x, const void* router_logits, int 
                                   size_t workspace_bytes, int64_t ar_handle, int64_t reg_buffer,
                                   int64_t reg_buffer_bytes, int ar_algo, int32_t* status_word, void* stream);
 
+/*
+ * All-reduce that ends in the NEXT decoder layer's residual add + RMSNorm, i.e. the reference's sequence
+ *   hidden = tensor_model_parallel_all_reduce(hidden)          (nanovllm/layers/fused_moe.py:614-624)
+ *   hidden, residual = input_layernorm(hidden, residual)       (nanovllm/models/qwen3_moe.py:262-270, ops.add_rms_norm)
+ * in one launch for messages the one-shot algorithm takes (a block reduces whole token rows over the ranks and
+ * normalises them; the reduced tensor never goes to memory), and as all-reduce into scratch_out + norm kernel for
+ * larger ones. Results are bit-identical to running the two steps. bf16 only.
+ *   inp bf16 [T, H] (staged into reg_buffer unless it is reg_buffer itself), residual bf16 [T, H] in/out,
+ *   norm_weight bf16 [H], normed_out bf16 [T, H], scratch_out bf16 [T, H] (may be NULL when T*H*2 bytes is within the
+ *   one-shot limit: 256 KiB at 8 ranks, 512 KiB at 4, any size at 2).
+ * The second form starts from the block's [T, k, H] slot tensor (k-slot sum fused in front); the third is
+ * moe_b200_fused_moe_forward_tp with that tail instead of the plain all-reduce.
+ */
+int moe_b200_ar_all_reduce_add_rms_norm(int64_t handle, const void* inp, void* scratch_out, void* residual,
+                                        const void* norm_weight, float eps, void* normed_out, int T, int H,
+                                        int64_t reg_buffer, int64_t reg_buffer_bytes, int algo, int32_t* status_word,
+                                        void* stream);
+int moe_b200_ar_moe_sum_all_reduce_add_rms_norm(int64_t handle, const void* c3, void* scratch_out, void* residual,
+                                                const void* norm_weight, float eps, void* normed_out, int T, int k,
+                                                int H, int64_t reg_buffer, int64_t reg_buffer_bytes, int algo,
+                                                int32_t* status_word, void* stream);
+int moe_b200_fused_moe_forward_tp_add_rms_norm(const void* x, const void* router_logits, int logits_is_bf16,
+                                               const void* w13, const void* w2, const void* w13_bias,
+                                               const void* w2_bias, void* residual, const void* norm_weight, float eps,
+                                               void* normed_out, void* scratch_out, int T, int E, int top_k, int H, int I,
+                                               int renormalize, int activation, void* workspace, size_t workspace_bytes,
+                                               int64_t ar_handle, int64_t reg_buffer, int64_t reg_buffer_bytes,
+                                               int ar_algo, int32_t* status_word, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

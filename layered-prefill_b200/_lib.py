@@ -81,6 +81,9 @@ SIGNATURES = {
     "moe_b200_ar_register_buffer": (c_int, [c_int64, POINTER(c_int64)]),
     "moe_b200_ar_all_reduce": (c_int, [c_int64, c_void_p, c_void_p, c_int64, c_int, c_int64, c_int64, c_int, c_void_p, c_void_p]),
     "moe_b200_ar_moe_sum_all_reduce": (c_int, [c_int64, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int, c_void_p, c_void_p]),
+    "moe_b200_ar_all_reduce_add_rms_norm": (c_int, [c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_int64, c_int64, c_int, c_void_p, c_void_p]),
+    "moe_b200_ar_moe_sum_all_reduce_add_rms_norm": (c_int, [c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int, c_void_p, c_void_p]),
+    "moe_b200_fused_moe_forward_tp_add_rms_norm": (c_int, [c_void_p, c_void_p, c_int] + [c_void_p] * 6 + [c_float, c_void_p, c_void_p] + [c_int] * 7 + [c_void_p, c_size_t, c_int64, c_int64, c_int64, c_int, c_void_p, c_void_p]),
     "moe_b200_ar_set_wait_limit_ns": (c_int, [c_int64, ctypes.c_uint64]),
     "moe_b200_ar_wait_probe": (c_int, [c_int64, ctypes.c_uint64, c_void_p, c_void_p]),
     "moe_b200_ar_graph_buffer_count": (c_int, [c_int64, POINTER(c_int)]),

@@ -28,6 +28,7 @@
 #include "launch.cuh"
 #include "moe_b200_internal.cuh"
 #include "ptx.cuh"
+#include "rms_norm_row.cuh"
 
 namespace moe_b200 {
 
@@ -196,6 +197,52 @@ __global__ void __launch_bounds__(kArThreads, 1) ar_oneshot_kernel(const ArParam
   peer_barrier<N>(p, true, &timed_out);
   uint4* out = static_cast<uint4*>(p.out);
   for (long long v = tid; v < p.nvec; v += stride) out[v] = reduce_ranks<T, N>(ptrs, v);
+  // nobody may overwrite its input while a peer still reads it
+  peer_barrier<N>(p, false, &timed_out);
+}
+
+// One-shot all-reduce that ends in the next layer's residual add + RMSNorm (what the decoder layer after the MoE
+// block does first with the reduced tensor: nanovllm/models/qwen3_moe.py:262-270, ops.add_rms_norm): a block owns
+// whole token rows, reduces a row over the ranks (fp32, rank order, bf16 rounding = the all-reduce's output), and
+// runs the norm's row code on it; the reduced tensor itself never goes to memory. Optional phase 0 as in the plain
+// kernel (k-slot sum into this rank's registered buffer).
+struct NormTail {
+  __nv_bfloat16* residual;      // [T, H], updated in place
+  const __nv_bfloat16* weight;  // [H]
+  __nv_bfloat16* normed;        // [T, H]
+  float eps;
+  int T;
+  int H;
+};
+
+template <int N>
+__global__ void __launch_bounds__(kArThreads, 1) ar_oneshot_add_rms_norm_kernel(const ArParams p, const NormTail nt) {
+  extern __shared__ uint4 ar_norm_smem[];
+  __shared__ bool timed_out;
+  if (threadIdx.x == 0) timed_out = false;
+  grid_dependency_launch();
+  grid_dependency_wait();
+  __nv_bfloat16* x_row = reinterpret_cast<__nv_bfloat16*>(ar_norm_smem);
+  float* red = reinterpret_cast<float*>(x_row + nt.H);
+  const RankData rd = *p.rank_data;
+  const uint4* ptrs[N];
+#pragma unroll
+  for (int r = 0; r < N; ++r) ptrs[r] = static_cast<const uint4*>(rd.ptrs[r]);
+  if (p.c3 != nullptr) {
+    const long long tid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    uint4* own = const_cast<uint4*>(ptrs[p.rank]);
+    for (long long v = tid; v < p.nvec; v += stride) slot_sum_vec(p, own, v);
+  }
+  peer_barrier<N>(p, true, &timed_out);
+  for (int row = blockIdx.x; row < nt.T; row += gridDim.x) {
+    const long long row_vec = static_cast<long long>(row) * (nt.H / 8);
+    const size_t off = static_cast<size_t>(row) * nt.H;
+    rms_norm_row<true, kArThreads, false>(
+        [&ptrs, row_vec](int c) { return reduce_ranks<__nv_bfloat16, N>(ptrs, row_vec + c / 8); }, nt.residual + off,
+        nt.weight, nt.normed + off, nt.H, nt.eps, x_row, red, red + 32, true);
+    __syncthreads();  // x_row and the reduction slots are reused by the next row
+  }
   // nobody may overwrite its input while a peer still reads it
   peer_barrier<N>(p, false, &timed_out);
 }
@@ -369,6 +416,49 @@ int ar_moe_sum_all_reduce_impl(int64_t handle, const void* c3, void* out, int T,
   return launch_ar<__nv_bfloat16>(*c, p, use_oneshot(*c, bytes, algo), stream);
 }
 
+// All-reduce (optionally with the k-slot sum in front) followed by residual add + RMSNorm. Small messages take the
+// fused one-shot kernel; anything else runs the all-reduce into `scratch_out` and the norm kernel after it.
+int ar_all_reduce_add_rms_norm_impl(int64_t handle, const void* c3, int k, void* scratch_out, __nv_bfloat16* residual,
+                                    const __nv_bfloat16* weight, float eps, __nv_bfloat16* normed, int T, int H,
+                                    int64_t reg_buffer, int64_t reg_buffer_bytes, int algo, int* status_word,
+                                    cudaStream_t stream) {
+  Comm* c = as_comm(handle);
+  if (c == nullptr) return set_error(kStatusInvalidArgument, "all_reduce_add_rms_norm: null communicator");
+  if (H % 8 != 0 || T < 0) return set_error(kStatusInvalidArgument, "all_reduce_add_rms_norm: H must be a multiple of 8");
+  if (T == 0) return kStatusOk;
+  const long long bytes = static_cast<long long>(T) * H * 2;
+  if (reg_buffer == 0 || reg_buffer_bytes < bytes)
+    return set_error(kStatusTooLarge, "all_reduce_add_rms_norm: registered buffer holds %lld bytes, %lld needed", static_cast<long long>(reg_buffer_bytes), bytes);
+  RankData* rd = nullptr;
+  if (int st = resolve_rank_data(*c, reinterpret_cast<const void*>(static_cast<intptr_t>(reg_buffer)), stream, &rd)) return st;
+  ArParams p{};
+  p.rank_data = rd; p.sg = c->sg; p.self_sg = c->self_sg; p.out = scratch_out; p.rank = c->rank;
+  p.nvec = bytes / 16; p.wait_limit_ns = c->wait_limit_ns; p.status = status_word;
+  p.c3 = static_cast<const __nv_bfloat16*>(c3); p.top_k = k; p.hidden_vecs = H / 8;
+  const size_t smem = static_cast<size_t>(H) * 2 + 40 * sizeof(float);
+  if (use_oneshot(*c, bytes, algo) && smem <= 48 * 1024) {
+    NormTail nt{residual, weight, normed, eps, T, H};
+    int blocks = T < kMaxArBlocks ? T : kMaxArBlocks;
+    if (blocks > device_sm_count()) blocks = device_sm_count();
+#define MOE_B200_ARN_CASE(n) \
+  case n: launch_pdl(ar_oneshot_add_rms_norm_kernel<n>, dim3(blocks), dim3(kArThreads), smem, stream, p, nt); break;
+    switch (c->world) {
+      MOE_B200_ARN_CASE(2)
+      MOE_B200_ARN_CASE(4)
+      MOE_B200_ARN_CASE(6)
+      MOE_B200_ARN_CASE(8)
+      default:
+        return set_error(kStatusInvalidArgument, "custom allreduce only supports num gpus in (2,4,6,8). Actual num gpus = %d", c->world);
+    }
+#undef MOE_B200_ARN_CASE
+    count_launches(1);
+    return check_launch("all_reduce_add_rms_norm");
+  }
+  if (scratch_out == nullptr) return set_error(kStatusInvalidArgument, "all_reduce_add_rms_norm: this size needs the scratch output");
+  if (int st = launch_ar<__nv_bfloat16>(*c, p, use_oneshot(*c, bytes, algo), stream)) return st;
+  return launch_rms_norm(normed, residual, static_cast<const __nv_bfloat16*>(scratch_out), weight, eps, T, H, stream);
+}
+
 }  // namespace moe_b200
 
 using namespace moe_b200;
@@ -499,6 +589,38 @@ int moe_b200_ar_moe_sum_all_reduce(int64_t handle, const void* c3, void* out, in
   if (c3 == nullptr || out == nullptr || status_word == nullptr) return set_error(kStatusInvalidArgument, "moe_sum_all_reduce: null pointer");
   return ar_moe_sum_all_reduce_impl(handle, c3, out, T, k, H, reg_buffer, reg_buffer_bytes, algo, status_word,
                                     static_cast<cudaStream_t>(stream));
+}
+
+int moe_b200_ar_all_reduce_add_rms_norm(int64_t handle, const void* inp, void* scratch_out, void* residual,
+                                        const void* norm_weight, float eps, void* normed_out, int T, int H,
+                                        int64_t reg_buffer, int64_t reg_buffer_bytes, int algo, int32_t* status_word,
+                                        void* stream_v) {
+  if (inp == nullptr || residual == nullptr || norm_weight == nullptr || normed_out == nullptr || status_word == nullptr)
+    return set_error(kStatusInvalidArgument, "all_reduce_add_rms_norm: null pointer");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  const long long bytes = static_cast<long long>(T) * H * 2;
+  if (reg_buffer == 0 || bytes > reg_buffer_bytes)
+    return set_error(kStatusTooLarge, "all_reduce_add_rms_norm: registered buffer is too small to contain the input");
+  void* reg = reinterpret_cast<void*>(static_cast<intptr_t>(reg_buffer));
+  if (inp != reg && bytes > 0) {
+    if (int st = check_cuda(cudaMemcpyAsync(reg, inp, static_cast<size_t>(bytes), cudaMemcpyDeviceToDevice, stream), "all_reduce staging copy")) return st;
+  }
+  return ar_all_reduce_add_rms_norm_impl(handle, nullptr, 0, scratch_out, static_cast<__nv_bfloat16*>(residual),
+                                         static_cast<const __nv_bfloat16*>(norm_weight), eps,
+                                         static_cast<__nv_bfloat16*>(normed_out), T, H, reg_buffer, reg_buffer_bytes, algo,
+                                         status_word, stream);
+}
+
+int moe_b200_ar_moe_sum_all_reduce_add_rms_norm(int64_t handle, const void* c3, void* scratch_out, void* residual,
+                                                const void* norm_weight, float eps, void* normed_out, int T, int k,
+                                                int H, int64_t reg_buffer, int64_t reg_buffer_bytes, int algo,
+                                                int32_t* status_word, void* stream) {
+  if (c3 == nullptr || residual == nullptr || norm_weight == nullptr || normed_out == nullptr || status_word == nullptr || k <= 0)
+    return set_error(kStatusInvalidArgument, "moe_sum_all_reduce_add_rms_norm: null pointer");
+  return ar_all_reduce_add_rms_norm_impl(handle, c3, k, scratch_out, static_cast<__nv_bfloat16*>(residual),
+                                         static_cast<const __nv_bfloat16*>(norm_weight), eps,
+                                         static_cast<__nv_bfloat16*>(normed_out), T, H, reg_buffer, reg_buffer_bytes, algo,
+                                         status_word, static_cast<cudaStream_t>(stream));
 }
 
 int moe_b200_ar_graph_buffer_count(int64_t handle, int* count_out) {

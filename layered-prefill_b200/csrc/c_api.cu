@@ -162,6 +162,10 @@ int run_experts_until_c3_ws(const void* x, const void* w13, const void* w2, cons
 // all_reduce.cu
 int ar_moe_sum_all_reduce_impl(int64_t handle, const void* c3, void* out, int T, int k, int H, int64_t reg_buffer,
                                int64_t reg_buffer_bytes, int algo, int* status_word, cudaStream_t stream);
+int ar_all_reduce_add_rms_norm_impl(int64_t handle, const void* c3, int k, void* scratch_out, __nv_bfloat16* residual,
+                                    const __nv_bfloat16* weight, float eps, __nv_bfloat16* normed, int T, int H,
+                                    int64_t reg_buffer, int64_t reg_buffer_bytes, int algo, int* status_word,
+                                    cudaStream_t stream);
 
 }  // namespace moe_b200
 
@@ -441,6 +445,39 @@ int moe_b200_fused_moe_forward_tp(const void* x, const void* router_logits, int 
     return st;
   return ar_moe_sum_all_reduce_impl(ar_handle, experts_workspace_c3(ews, T, E, top_k, H, I), out, T, top_k, H,
                                     reg_buffer, reg_buffer_bytes, ar_algo, status_word, s);
+}
+
+int moe_b200_fused_moe_forward_tp_add_rms_norm(const void* x, const void* router_logits, int logits_is_bf16,
+                                               const void* w13, const void* w2, const void* w13_bias,
+                                               const void* w2_bias, void* residual, const void* norm_weight, float eps,
+                                               void* normed_out, void* scratch_out, int T, int E, int top_k, int H, int I,
+                                               int renormalize, int activation, void* workspace, size_t workspace_bytes,
+                                               int64_t ar_handle, int64_t reg_buffer, int64_t reg_buffer_bytes,
+                                               int ar_algo, int32_t* status_word, void* stream) {
+  if (int st = check_block_shapes(T, E, top_k, H, I)) return st;
+  if (T == 0) return kStatusOk;
+  if (x == nullptr || router_logits == nullptr || w13 == nullptr || w2 == nullptr || residual == nullptr ||
+      norm_weight == nullptr || normed_out == nullptr || status_word == nullptr || ar_handle == 0)
+    return set_error(kStatusInvalidArgument, "fused_moe_forward_tp_add_rms_norm: null pointer or no communicator");
+  if (activation != MOE_B200_ACT_SILU && activation != MOE_B200_ACT_SWIGLUOAI)
+    return set_error(kStatusInvalidArgument, "fused_moe_forward_tp_add_rms_norm: unsupported activation code %d", activation);
+  const size_t need = moe_b200_fused_moe_workspace_bytes(T, E, top_k, H, I);
+  if (workspace == nullptr || workspace_bytes < need)
+    return set_error(kStatusWorkspaceTooSmall, "fused_moe_forward_tp_add_rms_norm: workspace of %zu bytes needed, %zu given", need, workspace_bytes);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  uint8_t* base = static_cast<uint8_t*>(workspace);
+  const size_t slot = align_up(sizeof(float) * static_cast<size_t>(T) * top_k);
+  float* tw = reinterpret_cast<float*>(base);
+  int32_t* ti = reinterpret_cast<int32_t*>(base + slot);
+  if (int st = launch_topk_softmax(router_logits, logits_is_bf16, tw, ti, nullptr, T, E, top_k, renormalize, s)) return st;
+  void* ews = base + 2 * slot;
+  if (int st = run_experts_until_c3_ws(x, w13, w2, w13_bias, w2_bias, tw, ti, T, E, top_k, H, I, activation, ews,
+                                       status_word, s))
+    return st;
+  return ar_all_reduce_add_rms_norm_impl(ar_handle, experts_workspace_c3(ews, T, E, top_k, H, I), top_k, scratch_out,
+                                         static_cast<__nv_bfloat16*>(residual), static_cast<const __nv_bfloat16*>(norm_weight),
+                                         eps, static_cast<__nv_bfloat16*>(normed_out), T, H, reg_buffer, reg_buffer_bytes,
+                                         ar_algo, status_word, s);
 }
 
 int moe_b200_read_status(const int32_t* status_word, int32_t* value, void* stream) {

@@ -20,6 +20,7 @@ import torch
 import torch.distributed as dist
 
 from . import ops
+from ._lib import check, lib
 
 MiB = 1024 * 1024
 DEFAULT_MAX_SIZE = 64 * MiB
@@ -148,6 +149,25 @@ class CustomAllreduce:
         else:
             ops.all_reduce(self._ptr, inp, out, self.buffer_ptrs[self.rank], self.max_size, algo)
         return out
+
+    def all_reduce_add_rms_norm(self, inp: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor, eps: float,
+                                *, algo: int = 0):
+        """all_reduce(inp) followed by the next layer's RMSNorm.forward(hidden, residual) (layers/layernorm.py:21-33),
+        one launch for decode-sized tensors. residual is updated in place; returns (normed, residual). Bit-identical
+        to the two separate steps."""
+        assert inp.dtype == torch.bfloat16 and inp.dim() == 2 and inp.is_contiguous()
+        assert residual.shape == inp.shape and residual.dtype == torch.bfloat16 and residual.is_contiguous()
+        T, H = inp.shape
+        normed = torch.empty_like(inp)
+        scratch = torch.empty_like(inp)
+        if T == 0:
+            return normed, residual
+        with torch.cuda.device(inp.device):
+            check(lib.moe_b200_ar_all_reduce_add_rms_norm(
+                self._ptr, inp.data_ptr(), scratch.data_ptr(), residual.data_ptr(), weight.data_ptr(), float(eps),
+                normed.data_ptr(), T, H, self.buffer_ptrs[self.rank], self.max_size, algo,
+                ops.status_word(inp.device).data_ptr(), torch.cuda.current_stream().cuda_stream))
+        return normed, residual
 
     def custom_all_reduce(self, input: torch.Tensor) -> Optional[torch.Tensor]:  # noqa: A002
         """custom_all_reduce.py:276-292."""

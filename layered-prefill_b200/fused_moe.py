@@ -131,6 +131,40 @@ def fused_experts_impl(hidden_states: torch.Tensor, w1: torch.Tensor, w2: torch.
     return out
 
 
+def fused_moe_forward_reduce_norm(hidden_states: torch.Tensor, router_logits: torch.Tensor, w13: torch.Tensor,
+                                  w2: torch.Tensor, top_k: int, residual: torch.Tensor, norm_weight: torch.Tensor,
+                                  eps: float, comm, renormalize: bool = True, activation: str = "silu",
+                                  w13_bias: Optional[torch.Tensor] = None, w2_bias: Optional[torch.Tensor] = None):
+    """Router + experts + tensor-parallel reduction + the NEXT decoder layer's input_layernorm(hidden, residual)
+    (nanovllm/models/qwen3_moe.py:99-116 followed by :262-270) through one library call; the k-slot sum, the
+    all-reduce and the add + norm are one kernel for decode-sized batches. residual is updated in place.
+    Returns (normed hidden states, residual)."""
+    T, H = hidden_states.shape
+    E, two_i, _ = w13.shape
+    inter = two_i // 2
+    assert comm is not None and not comm.disabled and comm.world_size > 1, "needs an initialised CustomAllreduce"
+    assert router_logits.shape == (T, E)
+    _check_experts_args(hidden_states, w13, w2, router_logits, router_logits, activation)
+    assert residual.shape == (T, H) and residual.dtype == torch.bfloat16 and residual.is_contiguous()
+    logits = router_logits if router_logits.dtype in (torch.bfloat16, torch.float32) else router_logits.float()
+    logits = logits.contiguous()
+    normed = torch.empty_like(hidden_states)
+    if T == 0:
+        return normed, residual
+    scratch = torch.empty_like(hidden_states)
+    dev = hidden_states.device
+    ws = _workspaces.get(dev, lib.moe_b200_fused_moe_workspace_bytes(T, E, top_k, H, inter))
+    with torch.cuda.device(dev):
+        check(lib.moe_b200_fused_moe_forward_tp_add_rms_norm(
+            hidden_states.data_ptr(), logits.data_ptr(), int(logits.dtype == torch.bfloat16), w13.data_ptr(),
+            w2.data_ptr(), w13_bias.data_ptr() if w13_bias is not None else 0,
+            w2_bias.data_ptr() if w2_bias is not None else 0, residual.data_ptr(), norm_weight.data_ptr(), float(eps),
+            normed.data_ptr(), scratch.data_ptr(), T, E, top_k, H, inter, int(bool(renormalize)), ACT_CODES[activation],
+            ws.data_ptr(), ws.numel(), comm._ptr, comm.buffer_ptrs[comm.rank], comm.max_size, 0,
+            ops.status_word(dev).data_ptr(), torch.cuda.current_stream().cuda_stream))
+    return normed, residual
+
+
 def _fused_experts_fp8(hidden_states, w1, w2, topk_weights, topk_ids, inplace, activation, w1_scale, w2_scale,
                        block_shape, w1_bias, w2_bias, a1_scale, a2_scale, w1_zp, w2_zp, expert_map,
                        apply_router_weight_on_input, out: Optional[torch.Tensor] = None) -> torch.Tensor:

@@ -196,6 +196,24 @@ class FusedMoE(torch.nn.Module):
         finally:
             self.reduce_results = saved
 
+    def forward_reduce_norm(self, hidden_states: torch.Tensor, router_logits: torch.Tensor, residual: torch.Tensor,
+                            norm_weight: torch.Tensor, eps: float):
+        """forward + all-reduce + the next decoder layer's input_layernorm(hidden, residual)
+        (nanovllm/models/qwen3_moe.py:262-270): returns (normed, residual) with residual updated in place. Falls back
+        to the separate steps when the tensor-parallel communicator cannot take the tensor."""
+        comm = _get_ar_communicator() if self.tp_size > 1 else None
+        usable = (comm is not None and not comm.disabled and hidden_states.numel() * 2 <= comm.max_size
+                  and self.custom_routing_function is None)
+        if usable:
+            return _fm.fused_moe_forward_reduce_norm(hidden_states, router_logits, self.w13_weight, self.w2_weight,
+                                                     self.top_k, residual, norm_weight, eps, comm, self.renormalize,
+                                                     self.activation, self._bias("w13_bias"), self._bias("w2_bias"))
+        out = self.forward_and_reduce(hidden_states, router_logits) if self.tp_size > 1 else self.forward(hidden_states, router_logits)
+        from . import ops as _ops
+        normed = torch.empty_like(out)
+        _ops.add_rms_norm(normed, residual, out, norm_weight, eps)
+        return normed, residual
+
     def extra_repr(self) -> str:
         return (f"global_num_experts={self.global_num_experts}, top_k={self.top_k}, "
                 f"intermediate_size_per_partition={self.intermediate_size_per_partition}, tp_size={self.tp_size}, "

@@ -3,7 +3,8 @@
 Checks, on every rank, against the CPU oracle:
   1. plain peer-memory all-reduce (one-shot and two-shot, staged and registered input) on several sizes;
   2. the fused k-slot-sum + all-reduce;
-  3. the whole tensor-parallel MoE block (I sharded as the reference's weight_loader does).
+  3. the whole tensor-parallel MoE block (I sharded as the reference's weight_loader does);
+  4. a graph-captured all-reduce; 5. the all-reduce that ends in the next layer's add + RMSNorm.
 Prints "TP_WORKER_OK rank=<r>" on success; any failure raises.
 """
 import os
@@ -124,6 +125,42 @@ def main():
         torch.cuda.synchronize()
         assert torch.all(res == sum(r + 1 + rep for r in range(world))), f"graph replay {rep}"
         dist.barrier()
+    assert ops.read_status(dev) == 0
+
+    # ---- 5. all-reduce that ends in the next layer's residual add + RMSNorm: same bits as the two steps, for a
+    # decode-sized tensor (one fused launch) and one above every one-shot limit (all-reduce + norm kernel)
+    for T, H in ((64, 2048), (1, 512), (33, 1024), (3000, 2048)):
+        parts, g = [], None
+        for r in range(world):
+            g = torch.Generator().manual_seed(T + 31 * r)
+            parts.append(torch.randn(T, H, generator=g).to(torch.bfloat16))
+        g = torch.Generator().manual_seed(T + 1000)
+        res0 = (torch.randn(T, H, generator=g) * 2).to(torch.bfloat16)
+        wn = (1 + 0.1 * torch.randn(H, generator=g)).to(torch.bfloat16).to(dev)
+        # the two separate steps
+        red = comm.all_reduce(parts[rank].to(dev), registered=False)
+        res_a, norm_a = res0.to(dev).clone(), torch.empty(T, H, dtype=torch.bfloat16, device=dev)
+        ops.add_rms_norm(norm_a, res_a, red, wn, 1e-6)
+        # one call
+        res_b = res0.to(dev).clone()
+        norm_b, res_b2 = comm.all_reduce_add_rms_norm(parts[rank].to(dev), res_b, wn, 1e-6)
+        torch.cuda.synchronize()
+        assert res_b2.data_ptr() == res_b.data_ptr()
+        assert torch.equal(res_a, res_b), f"residual T={T}"
+        assert torch.equal(norm_a, norm_b), f"normed T={T}"
+        assert torch.equal(red.cpu(), O.all_reduce(parts))
+    assert ops.read_status(dev) == 0
+    # the block with that tail, through the FusedMoE mirror: same bits as block -> all-reduce -> add_rms_norm
+    layer.reduce_results = True
+    res0 = (torch.randn(T := 96, H := 512, generator=torch.Generator().manual_seed(77)) * 2).to(torch.bfloat16)
+    wn = torch.ones(H, dtype=torch.bfloat16, device=dev)
+    blk = layer(x.to(dev).clone(), logits.to(dev))
+    res_a, norm_a = res0.to(dev).clone(), torch.empty_like(blk)
+    ops.add_rms_norm(norm_a, res_a, blk, wn, 1e-6)
+    res_b = res0.to(dev).clone()
+    norm_b, _ = layer.forward_reduce_norm(x.to(dev).clone(), logits.to(dev), res_b, wn, 1e-6)
+    torch.cuda.synchronize()
+    assert torch.equal(res_a, res_b) and torch.equal(norm_a, norm_b)
     assert ops.read_status(dev) == 0
 
     dist.barrier()
