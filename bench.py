@@ -643,6 +643,33 @@ def main():
             barrier()
             ar[f"T{t_ar}"] = max_over_ranks(a0.elapsed_time(a1)) / reps * 1e3
         extras["all_reduce_us_staged"] = ar
+        # the all-reduce followed by the next layer's residual add + RMSNorm: one call vs the two steps
+        if not mixed and wl.T <= 1024:
+            buf = torch.randn(wl.T, wl.H, device=dev).to(torch.bfloat16)
+            resid = torch.randn(wl.T, wl.H, device=dev).to(torch.bfloat16)
+            nw = torch.ones(wl.H, device=dev, dtype=torch.bfloat16)
+            nout = torch.empty_like(buf)
+
+            def two_steps():
+                ops.add_rms_norm(nout, resid, comm.all_reduce(buf), nw, 1e-6)
+
+            def one_call():
+                comm.all_reduce_add_rms_norm(buf, resid, nw, 1e-6)
+
+            tail = {}
+            for label, fn in (("all_reduce_then_add_rms_norm_us", two_steps), ("one_call_us", one_call)):
+                for _ in range(5):
+                    fn()
+                barrier()
+                a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                reps = 100
+                a0.record()
+                for _ in range(reps):
+                    fn()
+                a1.record()
+                barrier()
+                tail[label] = max_over_ranks(a0.elapsed_time(a1)) / reps * 1e3
+            extras["all_reduce_add_rms_norm"] = tail
     if mixed:
         extras["mixed_iteration"] = {"layers": MIXED_LAYERS, "group_layers": MIXED_GROUP, "decode_tokens": MIXED_DECODE_T,
                                      "prefill_tokens": MIXED_PREFILL_T, "moe_path_us_per_iteration": ms_per_step * 1e3}
