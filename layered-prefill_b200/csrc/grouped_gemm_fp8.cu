@@ -10,7 +10,7 @@
 // TMA (byte tensor map, 128-byte swizzle), token rows by cp.async, one MMA thread, static tile list. What
 // differs: a shared-memory stage holds 128 K elements = exactly one scale block, so the tensor core cannot
 // accumulate across stages. Each stage's product (4 tcgen05.mma kind::f8f6f4, K = 32 each) goes into one of
-// two 128-column TMEM buffers, and eight warps (two per TMEM lane quarter, 64 accumulator columns each) read it
+// four 128-column TMEM buffers, and eight warps (two per TMEM lane quarter, 64 accumulator columns each) read it
 // back, multiply by the two scales and accumulate in registers; the same warps then run the epilogue (SiLU * up
 // with the bf16 kernels' rounding points, or x routed weight). The first purpose is the weight-streaming
 // regime, where halving the bytes halves the time; at prefill sizes the register accumulation costs about as
@@ -36,7 +36,8 @@ constexpr int kStageB = 128 * kGroup;  // 16 KB of weight rows (64 gate + 64 up,
 constexpr int kStageBytes = kStageA + kStageB;
 constexpr int kStages = 6;
 constexpr int kPartCols = 128;         // accumulator columns per stage product
-constexpr int kTmemCols = 256;         // two of them
+constexpr int kPartBufs = 4;           // stage products in flight between the MMA thread and the accumulating warps
+constexpr int kTmemCols = kPartBufs * kPartCols;
 constexpr int kBarrierBytes = 1024;
 constexpr int kSmemBytes = kBarrierBytes + 1024 /*alignment slack*/ + kStages * kStageBytes;
 
@@ -82,8 +83,8 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_b, const Params
   uint64_t* bar_full = reinterpret_cast<uint64_t*>(smem);
   uint64_t* bar_empty = bar_full + kStages;
   uint64_t* bar_part_full = bar_empty + kStages;
-  uint64_t* bar_part_free = bar_part_full + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_part_free + 2);
+  uint64_t* bar_part_free = bar_part_full + kPartBufs;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_part_free + kPartBufs);
   uint8_t* ring = smem + kBarrierBytes;
 
   const int warp = threadIdx.x >> 5;
@@ -94,7 +95,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_b, const Params
       mbar_init(&bar_full[s], 1 + 128);
       mbar_init(&bar_empty[s], 1);
     }
-    for (int b = 0; b < 2; ++b) {
+    for (int b = 0; b < kPartBufs; ++b) {
       mbar_init(&bar_part_full[b], 1);
       mbar_init(&bar_part_free[b], 8);
     }
@@ -155,8 +156,8 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_b, const Params
       bool ok = true;
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
         for (int kb = 0; kb < num_kb; ++kb, ++j) {
-          const uint32_t b = j & 1u;
-          const uint32_t bph = (j >> 1) & 1u;
+          const uint32_t b = j % kPartBufs;
+          const uint32_t bph = (j / kPartBufs) & 1u;
           if (!mbar_wait(&bar_part_free[b], bph ^ 1u)) {
             report(p.status, kErrWaitTmemEmpty);
             ok = false;
@@ -218,8 +219,8 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_b, const Params
       float w0_n = __ldg(w_s0);
       float w1_n = kMode == 1 ? __ldg(w_s1) : 0.f;
       for (int kb = 0; kb < num_kb; ++kb, ++j) {
-        const uint32_t b = j & 1u;
-        const uint32_t bph = (j >> 1) & 1u;
+        const uint32_t b = j % kPartBufs;
+        const uint32_t bph = (j / kPartBufs) & 1u;
         const float s0 = sa_n * w0_n;
         const float s1 = kMode == 1 ? sa_n * w1_n : s0;
         if (kb + 1 < num_kb) {
