@@ -99,3 +99,51 @@ def test_fp8_rejects_what_it_does_not_build():
                                 w2_scale=torch.ones(2, 2, 1, device=d), block_shape=[128, 128])
     with pytest.raises(ValueError):   # scales missing
         fused_moe.fused_experts(x, w13, w2, None, None, tw, ti)
+
+
+def test_fp8_block_with_the_steps_in_front_replays_from_a_cuda_graph():
+    """pre_moe (cluster kernel) + fp8 experts captured once and replayed on new inputs in the same buffers."""
+    from layered_prefill_b200 import fused_moe
+    g = torch.Generator().manual_seed(31)
+    T, H, E, k, I = 48, 512, 128, 8, 128
+    d = _dev()
+    w13 = (torch.randn(E, 2 * I, H, generator=g) * 0.02).to(torch.bfloat16)
+    w2 = (torch.randn(E, H, I, generator=g) * 0.02).to(torch.bfloat16)
+    q13, s13 = O.quant_weight_block_fp8(w13)
+    q2, s2 = O.quant_weight_block_fp8(w2)
+    wg = (torch.randn(E, H, generator=g) * 0.05).to(torch.bfloat16)
+    nw = (1 + 0.1 * torch.randn(H, generator=g)).to(torch.bfloat16)
+    attn = [torch.randn(T, H, generator=g).to(torch.bfloat16) for _ in range(2)]
+    res = [torch.randn(T, H, generator=g).to(torch.bfloat16) for _ in range(2)]
+    a_buf, r_buf = attn[0].to(d), res[0].to(d)
+    q13d, s13d, q2d, s2d, wgd, nwd = (t.to(d) for t in (q13, s13, q2, s2, wg, nw))
+
+    def step():
+        normed, _, tw, ti = fused_moe.pre_moe(a_buf, r_buf, nwd, 1e-6, wgd, k, True)
+        return fused_moe.fused_experts(normed, q13d, q2d, None, None, tw, ti, inplace=False, w1_scale=s13d,
+                                       w2_scale=s2d, block_shape=[128, 128])
+
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(2):
+            r_buf.copy_(res[0])
+            step()
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        out = step()
+    for i in (1, 0):
+        a_buf.copy_(attn[i])
+        r_buf.copy_(res[i])
+        graph.replay()
+        torch.cuda.synchronize()
+        normed, r_new = O.add_rms_norm(attn[i], res[i], nw, 1e-6)
+        assert torch.equal(r_buf.cpu(), r_new)
+        logits = O.router_gate(normed, wg)
+        tw, ti, _ = O.fused_topk(normed, logits, k, True)
+        want = O.fused_experts_fp8(normed, q13, s13, q2, s2, tw, ti)
+        # the gate logits' summation order is free: on a near-tie the routing may differ from the CPU's, so the
+        # comparison uses the tolerance of the dequantised path rather than the emulation's
+        assert O.rel_l2(out.cpu(), want) <= REL_L2_DEQUANT
+    _status_ok()
