@@ -36,9 +36,7 @@ namespace {
 
 constexpr int BM = kBlockM;
 constexpr int BK = 64;  // bf16 elements per K block = one 128-byte swizzle row
-constexpr int kUmmaK = 16;
 constexpr int kMaxStages = 8;
-constexpr int kMaxBN = 256;
 constexpr int kABytes = BM * BK * 2;
 constexpr int kAccCols = 256;
 constexpr int kTmemCols = 512;
