@@ -66,7 +66,9 @@ __device__ __forceinline__ void stable_place_chunk(const int* __restrict__ topk_
   const int rank = __popc(peers & ((1u << lane) - 1u));
   const int leader = __ffs(peers) - 1;
   int slot = 0;
-  for (int w = 0; w < kThreads / 32; ++w) {
+  // warps past the end of the input hold no index: the turn-taking stops at the last warp that does
+  const int live_warps = min(kThreads / 32, (numel - base + 31) / 32);
+  for (int w = 0; w < live_warps; ++w) {
     if (warp == w) {
       if (e >= 0 && lane == leader) {
         slot = running[e];
