@@ -263,8 +263,8 @@ def main():
         if comm.disabled:
             raise SystemExit("peer-memory all-reduce could not be initialised on this box")
 
-    if args.fp8 and (world > 1 or mixed):
-        raise SystemExit("--fp8 runs the single-GPU block only")
+    if args.fp8 and mixed:
+        raise SystemExit("--fp8 runs the single block workloads only")
     prefill = wl.T >= 2048
     steps = args.steps if args.steps is not None else (20 if mixed else 200 if prefill else 2000)
     warmup = args.warmup if args.warmup is not None else (3 if mixed else 10 if prefill else 50)
@@ -297,8 +297,14 @@ def main():
                 return blocks.clamp(-448, 448).to(torch.float8_e4m3fn).view(e, n, k).contiguous(), sc
             q13, s13 = quantise(w13_full)
             q2, s2 = quantise(w2_full)
-            sets.append((q13, q2, s13, s2))
             del w13_full, w2_full
+            if tp > 1:  # this rank's slice of I; the scales stay those of the unsharded weights
+                lo, hi = rank * ip, (rank + 1) * ip
+                b13, b2 = q13.view(torch.uint8), q2.view(torch.uint8)
+                q13 = torch.cat([b13[:, lo:hi], b13[:, wl.I + lo:wl.I + hi]], dim=1).contiguous().view(torch.float8_e4m3fn)
+                q2 = b2[:, :, lo:hi].contiguous().view(torch.float8_e4m3fn)
+                del b13, b2
+            sets.append((q13, q2, s13, s2))
         elif tp == 1:
             sets.append((w13_full, w2_full))
         else:
@@ -308,11 +314,16 @@ def main():
             del w13_full, w2_full
     torch.cuda.synchronize()
     out = torch.empty_like(x)
+    fp8_partial = torch.empty_like(x) if (args.fp8 and tp > 1) else None
 
     def block(i, xin, lgin, dst):
         if args.fp8:
             q13, q2, s13, s2 = sets[i % n_sets]
-            return fused_moe.fused_moe_forward_fp8(xin, lgin, q13, s13, q2, s2, wl.top_k, True, out=dst)
+            if tp == 1:
+                return fused_moe.fused_moe_forward_fp8(xin, lgin, q13, s13, q2, s2, wl.top_k, True, out=dst)
+            tw_, ti_, _ = fused_moe.fused_topk(xin, lgin, wl.top_k, True)
+            part = fused_moe.fused_experts_fp8_shard(xin, q13, s13, q2, s2, tw_, ti_, rank * ip, wl.I, out=fp8_partial)
+            return comm.all_reduce(part, out=dst)
         w13, w2 = sets[i % n_sets]
         return fused_moe.fused_moe_forward(xin, lgin, w13, w2, wl.top_k, True, "silu", inplace=False, comm=comm,
                                            out=dst)
@@ -532,8 +543,8 @@ def main():
                      "peak_source": f"of {peaks['source']}", "launches_timed": k_iters})
     if args.fp8:
         # the fp8 kernels have no stand-alone entry point: the whole block against the HBM stream of its fp8 bytes
-        f8_bytes = (n_active * 3 * wl.H * wl.I * (1 + 4 / 16384) + wl.T * wl.H * (2 + 1 + 2)
-                    + wl.T * wl.top_k * (wl.I * (2 + 2 + 1 + 1) + wl.H * 4))
+        f8_bytes = (n_active * 3 * wl.H * ip * (1 + 4 / 16384) + wl.T * wl.H * (2 + 1 + 2)
+                    + wl.T * wl.top_k * (ip * (2 + 2 + 1 + 1) + wl.H * 4))
         achieved = f8_bytes / (ms_per_step * 1e-3) / 1e9
         roofline = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                     "frac": achieved / peaks["hbm_gbs"], "traffic": None,
@@ -694,7 +705,8 @@ def main():
                        "tensor_parallel": tp, "I_per_rank": ip,
                        "launch": "cuda graph replay per step" if use_graph else "eager launches",
                        "l2": f"weights rotate over {n_sets} distinct copies ({n_sets * 3 * wl.E * wl.H * ip * (1 if args.fp8 else 2) / 1e6:.0f} MB per rank) so no step finds them in L2",
-                       "all_reduce": "fused k-slot sum + peer-memory all-reduce" if world > 1 else "none (1 GPU)"},
+                       "all_reduce": ("none (1 GPU)" if world == 1 else "k-slot sum kernel, then peer-memory all-reduce" if args.fp8
+                                      else "fused k-slot sum + peer-memory all-reduce")},
             "us_per_layer": ms_per_step * 1e3, "tokens_per_s": wl.T / (ms_per_step * 1e-3),
             "roofline": roofline, "block": block_stats, "cpu_baseline": cpu_baseline, "e2e": e2e,
             "gpu_launches": launches, "clocks": clocks,

@@ -160,13 +160,23 @@ int moe_b200_fused_experts(const void* x, const void* w13, const void* w2, const
  *   w13_q      e4m3 [E, 2*I, H] (one byte each), w13_scale fp32 [E, 2*I/128, H/128]
  *   w2_q       e4m3 [E, H, I],                   w2_scale  fp32 [E, H/128, I/128]
  *   out        bf16 [T, H]
- * Requires H % 128 == 0 and I % 128 == 0 (I = the intermediate size held by this rank); SiLU only, no biases.
+ * Requires H % 128 == 0 and I % 128 == 0; SiLU only, no biases.
  */
 size_t moe_b200_fused_experts_fp8_workspace_bytes(int T, int E, int top_k, int H, int I);
 int moe_b200_fused_experts_fp8(const void* x, const void* w13_q, const float* w13_scale, const void* w2_q,
                                const float* w2_scale, const float* topk_weights, const int32_t* topk_ids, void* out,
                                int T, int E, int top_k, int H, int I, void* workspace, size_t workspace_bytes,
                                int32_t* status_word, void* stream);
+/* The same on one tensor-parallel rank: this rank holds the slice [i_offset, i_offset + I) of an intermediate
+ * dimension of i_total (w13_q [E, 2*I, H] = its gate rows then its up rows, w2_q [E, H, I]); the scales stay those
+ * of the unsharded weights (w13_scale [E, 2*i_total/128, H/128], w2_scale [E, H/128, i_total/128]) and are indexed
+ * by global position, so a slice may start or end inside a scale block (I = 192 at TP=8 of I = 1536). The
+ * intermediate is quantised in groups that follow those blocks. out = this rank's partial sum (all-reduce it).
+ * Requires i_total % 128 == 0, I % 64 == 0, i_offset % 64 == 0. */
+int moe_b200_fused_experts_fp8_tp(const void* x, const void* w13_q, const float* w13_scale, const void* w2_q,
+                                  const float* w2_scale, const float* topk_weights, const int32_t* topk_ids, void* out,
+                                  int T, int E, int top_k, int H, int I, int i_offset, int i_total, void* workspace,
+                                  size_t workspace_bytes, int32_t* status_word, void* stream);
 /* q[r, c] = e4m3(x[r, c] / s[r, c/128]), s[r, g] = max(|x[r, 128g .. 128g+127]|, 1e-10) / 448; x bf16 [rows, cols],
  * cols % 128 == 0. The activation quantisation the call above applies (exposed for tests and for callers
  * that keep quantised activations). */

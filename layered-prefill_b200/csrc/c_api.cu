@@ -107,7 +107,7 @@ Fp8Workspace carve_fp8(void* ws, int T, int E, int top_k, int H, int I) {
   w.x_q = p + off; off += align_up(rows_t * H);
   w.x_s = reinterpret_cast<float*>(p + off); off += align_up(sizeof(float) * rows_t * ((H + 127) / 128));
   w.h_q = p + off; off += align_up(rows_p * I);
-  w.h_s = reinterpret_cast<float*>(p + off); off += align_up(sizeof(float) * rows_p * ((I + 127) / 128));
+  w.h_s = reinterpret_cast<float*>(p + off); off += align_up(sizeof(float) * rows_p * ((I + 127) / 128 + 1));
   w.total = off;
   return w;
 }
@@ -343,7 +343,7 @@ int moe_b200_add_rms_norm_router(const void* input, void* residual, const void* 
 
 int moe_b200_quant_fp8_per_token_group(const void* x, int rows, int cols, void* q, float* scales, void* stream) {
   if (x == nullptr || q == nullptr || scales == nullptr) return set_error(kStatusInvalidArgument, "quant_fp8_per_token_group: null pointer");
-  return launch_quant_rows_fp8(static_cast<const __nv_bfloat16*>(x), rows, cols, static_cast<uint8_t*>(q), scales, nullptr,
+  return launch_quant_rows_fp8(static_cast<const __nv_bfloat16*>(x), rows, cols, 0, static_cast<uint8_t*>(q), scales, nullptr,
                                0, nullptr, static_cast<cudaStream_t>(stream));
 }
 
@@ -352,13 +352,13 @@ size_t moe_b200_fused_experts_fp8_workspace_bytes(int T, int E, int top_k, int H
   return carve_fp8(nullptr, T, E, top_k, H, I).total;
 }
 
-int moe_b200_fused_experts_fp8(const void* x, const void* w13_q, const float* w13_scale, const void* w2_q,
-                               const float* w2_scale, const float* topk_weights, const int32_t* topk_ids, void* out,
-                               int T, int E, int top_k, int H, int I, void* workspace, size_t workspace_bytes,
-                               int32_t* status_word, void* stream) {
+int moe_b200_fused_experts_fp8_tp(const void* x, const void* w13_q, const float* w13_scale, const void* w2_q,
+                                  const float* w2_scale, const float* topk_weights, const int32_t* topk_ids, void* out,
+                                  int T, int E, int top_k, int H, int I, int i_offset, int i_total, void* workspace,
+                                  size_t workspace_bytes, int32_t* status_word, void* stream) {
   if (int st = check_block_shapes(T, E, top_k, H, I)) return st;
-  if (H % 128 != 0 || I % 128 != 0)
-    return set_error(kStatusInvalidArgument, "fused_experts_fp8: H and the per-rank I must be multiples of 128 (H=%d I=%d)", H, I);
+  if (H % 128 != 0 || I % 64 != 0 || i_total % 128 != 0 || i_offset % 64 != 0 || i_offset < 0 || i_offset + I > i_total)
+    return set_error(kStatusInvalidArgument, "fused_experts_fp8: H must be a multiple of 128, the intermediate size %d of 128, this rank's slice [%d, %d) of 64 (H=%d)", i_total, i_offset, i_offset + I, H);
   if (T == 0) return kStatusOk;
   if (x == nullptr || w13_q == nullptr || w13_scale == nullptr || w2_q == nullptr || w2_scale == nullptr ||
       topk_weights == nullptr || topk_ids == nullptr || out == nullptr || status_word == nullptr)
@@ -369,7 +369,7 @@ int moe_b200_fused_experts_fp8(const void* x, const void* w13_q, const float* w1
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const Fp8Workspace w = carve_fp8(workspace, T, E, top_k, H, I);
   const PermSizes ps = perm_sizes(T, E, top_k);
-  if (int st = launch_quant_rows_fp8(static_cast<const __nv_bfloat16*>(x), T, H, w.x_q, w.x_s, nullptr, 0, nullptr, s)) return st;
+  if (int st = launch_quant_rows_fp8(static_cast<const __nv_bfloat16*>(x), T, H, 0, w.x_q, w.x_s, nullptr, 0, nullptr, s)) return st;
   if (int st = launch_align_block_size(topk_ids, ps.numel, E, kBlockM, w.base.sorted_ids, ps.sorted_cap, w.base.expert_ids,
                                        ps.blocks_cap, w.base.num_post_pad, w.base.align_ws, w.base.align_ws_bytes, s))
     return st;
@@ -377,13 +377,24 @@ int moe_b200_fused_experts_fp8(const void* x, const void* w13_q, const float* w1
   a.sorted_ids = w.base.sorted_ids; a.expert_ids = w.base.expert_ids; a.num_post_pad = w.base.num_post_pad;
   a.numel = ps.numel; a.top_k = top_k; a.max_m_blocks = ps.blocks_cap; a.num_experts = E;
   a.hidden = H; a.inter = I; a.activation = 0; a.status = status_word;
-  if (int st = launch_grouped_gemm1_fp8(a, w.x_q, w.x_s, static_cast<const uint8_t*>(w13_q), w13_scale, w.base.h_sorted, s)) return st;
-  if (int st = launch_quant_rows_fp8(w.base.h_sorted, ps.sorted_cap, I, w.h_q, w.h_s, w.base.sorted_ids, ps.numel,
-                                     w.base.num_post_pad, s))
+  if (int st = launch_grouped_gemm1_fp8(a, w.x_q, w.x_s, static_cast<const uint8_t*>(w13_q), w13_scale, i_offset, i_total,
+                                        w.base.h_sorted, s))
     return st;
-  if (int st = launch_grouped_gemm2_fp8(a, w.h_q, w.h_s, static_cast<const uint8_t*>(w2_q), w2_scale, topk_weights, w.base.c3, s))
+  if (int st = launch_quant_rows_fp8(w.base.h_sorted, ps.sorted_cap, I, i_offset % 128, w.h_q, w.h_s, w.base.sorted_ids,
+                                     ps.numel, w.base.num_post_pad, s))
+    return st;
+  if (int st = launch_grouped_gemm2_fp8(a, w.h_q, w.h_s, static_cast<const uint8_t*>(w2_q), w2_scale, i_offset, i_total,
+                                        topk_weights, w.base.c3, s))
     return st;
   return launch_moe_sum(w.base.c3, static_cast<__nv_bfloat16*>(out), T, top_k, H, s);
+}
+
+int moe_b200_fused_experts_fp8(const void* x, const void* w13_q, const float* w13_scale, const void* w2_q,
+                               const float* w2_scale, const float* topk_weights, const int32_t* topk_ids, void* out,
+                               int T, int E, int top_k, int H, int I, void* workspace, size_t workspace_bytes,
+                               int32_t* status_word, void* stream) {
+  return moe_b200_fused_experts_fp8_tp(x, w13_q, w13_scale, w2_q, w2_scale, topk_weights, topk_ids, out, T, E, top_k, H,
+                                       I, 0, I, workspace, workspace_bytes, status_word, stream);
 }
 
 size_t moe_b200_fused_moe_workspace_bytes(int T, int E, int top_k, int H, int I) {

@@ -53,8 +53,15 @@ struct ParamsF8 {
   const int* num_post_pad;
   const uint8_t* a_q;  // [T, K] (gate_up: indexed by token) or [rows, K] (down: indexed by permuted row)
   const float* a_s;    // [.., K / 128]
-  const float* w_s;    // [E, w_s_rows, K / 128]
+  const float* w_s;    // [E, w_s_rows, w_s_ld]: the UNSHARDED scale tensor, indexed by global block
   int w_s_rows;
+  int w_s_ld;
+  int a_s_ld;          // scale groups per activation row = K blocks of this launch
+  int num_kb;
+  int k_shift;         // columns by which this rank's K range starts inside a scale block (0 unless K is sharded)
+  int w_kb_off;        // global index of this rank's first K block
+  int row_blk0;        // scale-row block of this tile family's first weight row (gate half, or the down rows)
+  int row_blk1;        // same for the up half
   int numel;
   int top_k;
   int K;
@@ -115,7 +122,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_b, const Params
 
   const int num_m_blocks = *p.num_post_pad / BM;
   const int total_tiles = num_m_blocks * p.n_tiles;
-  const int num_kb = p.K / kGroup;
+  const int num_kb = p.num_kb;
 
   if (warp == kWarpTma) {
     // ------------------------------------------------------------------ TMA producer (weights)
@@ -135,10 +142,12 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_b, const Params
           uint8_t* b_dst = ring + s * kStageBytes + kStageA;
           mbar_arrive_expect_tx(&bar_full[s], kStageB);
           if (kMode == 1) {
-            tma_load_3d(b_dst, &tmap_b, kb * kGroup, n0, e, &bar_full[s]);
-            tma_load_3d(b_dst + 64 * kGroup, &tmap_b, kb * kGroup, p.inter + n0, e, &bar_full[s]);
+            tma_load_3d(b_dst, &tmap_b, kb * kGroup - p.k_shift, n0, e, &bar_full[s]);
+            tma_load_3d(b_dst + 64 * kGroup, &tmap_b, kb * kGroup - p.k_shift, p.inter + n0, e, &bar_full[s]);
           } else {
-            tma_load_3d(b_dst, &tmap_b, kb * kGroup, n0, e, &bar_full[s]);
+            // a sharded K range may start inside a scale block: the box then begins at a negative (16-byte aligned)
+            // coordinate and the part outside the tensor is zero-filled
+            tma_load_3d(b_dst, &tmap_b, kb * kGroup - p.k_shift, n0, e, &bar_full[s]);
           }
           if (++s == kStages) {
             s = 0;
@@ -193,7 +202,6 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_b, const Params
     const int q = warp & 3;                        // TMEM lane quarter this warp may read
     const int hf = (warp - kWarpPromote0) >> 2;    // which half of the tile's output columns
     const int row_in_tile = q * 32 + lane;
-    const int scale_ld = p.K / kGroup;
     uint32_t j = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
@@ -205,9 +213,10 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_b, const Params
       const bool valid = flat < p.numel;
       const bool any_valid = __any_sync(0xffffffffu, valid);
       const float* a_s_row =
-          p.a_s + (kMode == 1 ? static_cast<long long>(valid ? flat / p.top_k : 0) : (valid ? pos : 0)) * scale_ld;
-      const float* w_s0 = p.w_s + (static_cast<long long>(e) * p.w_s_rows + n0 / kGroup) * scale_ld;
-      const float* w_s1 = p.w_s + (static_cast<long long>(e) * p.w_s_rows + (p.inter + n0) / kGroup) * scale_ld;
+          p.a_s + (kMode == 1 ? static_cast<long long>(valid ? flat / p.top_k : 0) : (valid ? pos : 0)) * p.a_s_ld;
+      // weight scales by global position: row block of (rank offset + n0), K block of (rank's first block + kb)
+      const float* w_s0 = p.w_s + (static_cast<long long>(e) * p.w_s_rows + (p.row_blk0 + n0) / kGroup) * p.w_s_ld + p.w_kb_off;
+      const float* w_s1 = p.w_s + (static_cast<long long>(e) * p.w_s_rows + (p.row_blk1 + n0) / kGroup) * p.w_s_ld + p.w_kb_off;
 
       float acc[64];
 #pragma unroll
@@ -310,9 +319,9 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_b, const Params
         const long long pos = static_cast<long long>(m_blk) * BM + row0 + 16 * i;
         const int flat = p.sorted_ids[pos];
         if (kMode == 1)
-          src[i] = flat < p.numel ? p.a_q + static_cast<long long>(flat / p.top_k) * p.K + ch * 16 : nullptr;
+          src[i] = flat < p.numel ? p.a_q + static_cast<long long>(flat / p.top_k) * p.K : nullptr;
         else
-          src[i] = flat < p.numel ? p.a_q + pos * p.K + ch * 16 : nullptr;
+          src[i] = flat < p.numel ? p.a_q + pos * p.K : nullptr;
       }
       for (int kb = 0; kb < num_kb; ++kb) {
         ok = mbar_wait(&bar_empty[s], ph ^ 1u);
@@ -322,12 +331,13 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_b, const Params
           break;
         }
         const uint32_t a_base = smem_u32(ring + s * kStageBytes);
+        const int col = kb * kGroup - p.k_shift + ch * 16;  // this lane's 16 columns of the stage, in the rank's K range
+        const bool in_k = col >= 0 && col + 16 <= p.K;
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           const uint32_t dst = a_base + static_cast<uint32_t>(row0 + 16 * i) * 128u + swz;
-          const bool live = src[i] != nullptr;
-          cp_async_16(dst, live ? static_cast<const void*>(src[i] + kb * kGroup) : static_cast<const void*>(p.a_q),
-                      live ? 16u : 0u);
+          const bool live = in_k && src[i] != nullptr;
+          cp_async_16(dst, live ? static_cast<const void*>(src[i] + col) : static_cast<const void*>(p.a_q), live ? 16u : 0u);
         }
         cp_async_mbar_arrive_noinc(&bar_full[s]);
         if (++s == kStages) {
@@ -378,7 +388,7 @@ quant_rows_fp8_kernel(const __nv_bfloat16* __restrict__ x, int rows, int cols, u
 // valid rows come first (the permutation pads each expert at the end), so the CTA counts them once and its warps
 // walk (valid row, group) pairs only; decode batches have ~4 valid rows in a block of 128.
 __global__ void __launch_bounds__(256)
-quant_permuted_rows_fp8_kernel(const __nv_bfloat16* __restrict__ x, int cols, uint8_t* __restrict__ q,
+quant_permuted_rows_fp8_kernel(const __nv_bfloat16* __restrict__ x, int cols, int shift, uint8_t* __restrict__ q,
                                float* __restrict__ s, const int* __restrict__ sorted_ids, int numel,
                                const int* __restrict__ num_post_pad) {
   grid_dependency_launch();
@@ -386,13 +396,18 @@ quant_permuted_rows_fp8_kernel(const __nv_bfloat16* __restrict__ x, int cols, ui
   const int blk = blockIdx.x;
   if (blk * BM >= *num_post_pad) return;
   const int n_valid = __syncthreads_count(threadIdx.x < BM && sorted_ids[blk * BM + threadIdx.x] < numel);
-  const int groups = cols / kGroup;
+  // group g covers columns [128 g - shift, 128 (g + 1) - shift) of the row, cut to [0, cols): with a sharded
+  // intermediate dimension the groups follow the scale blocks of the unsharded tensor
+  const int groups = (shift + cols + kGroup - 1) / kGroup;
   const int lane = threadIdx.x & 31;
   // gridDim.y CTAs share a block's tasks (prefill-sized batches: up to 128 valid rows per block)
   for (int task = (threadIdx.x >> 5) + 8 * blockIdx.y; task < n_valid * groups; task += 8 * gridDim.y) {
     const long long row = static_cast<long long>(blk) * BM + task / groups;
     const int g = task % groups;
-    const uint2 raw = *reinterpret_cast<const uint2*>(x + row * cols + g * kGroup + lane * 4);
+    const int c = g * kGroup - shift + lane * 4;
+    const bool in = c >= 0 && c + 4 <= cols;
+    uint2 raw = make_uint2(0u, 0u);
+    if (in) raw = *reinterpret_cast<const uint2*>(x + row * cols + c);
     const __nv_bfloat162 p0 = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
     const __nv_bfloat162 p1 = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
     const float v[4] = {__low2float(p0), __high2float(p0), __low2float(p1), __high2float(p1)};
@@ -404,7 +419,7 @@ quant_permuted_rows_fp8_kernel(const __nv_bfloat16* __restrict__ x, int cols, ui
 #pragma unroll
     for (int i = 0; i < 4; ++i)
       packed |= static_cast<uint32_t>(__nv_cvt_float_to_fp8(v[i] / scale, __NV_SATFINITE, __NV_E4M3)) << (8 * i);
-    *reinterpret_cast<uint32_t*>(q + row * cols + g * kGroup + lane * 4) = packed;
+    if (in) *reinterpret_cast<uint32_t*>(q + row * cols + c) = packed;
     if (lane == 0) s[row * groups + g] = scale;
   }
 }
@@ -420,9 +435,11 @@ int ensure_smem_attr_f8() {
   return kStatusOk;
 }
 
-int check_fp8_shapes(const GroupedGemmArgs& a) {
-  if (a.hidden <= 0 || a.inter <= 0 || a.hidden % kGroup != 0 || a.inter % kGroup != 0)
-    return set_error(kStatusInvalidArgument, "fp8 grouped GEMM: hidden and the per-rank intermediate size must be multiples of %d (got %d, %d)", kGroup, a.hidden, a.inter);
+int check_fp8_shapes(const GroupedGemmArgs& a, int i_offset, int i_total) {
+  if (a.hidden <= 0 || a.inter <= 0 || a.hidden % kGroup != 0 || a.inter % 64 != 0)
+    return set_error(kStatusInvalidArgument, "fp8 grouped GEMM: hidden must be a multiple of %d and the per-rank intermediate size of 64 (got %d, %d)", kGroup, a.hidden, a.inter);
+  if (i_total % kGroup != 0 || i_offset < 0 || i_offset % 64 != 0 || i_offset + a.inter > i_total)
+    return set_error(kStatusInvalidArgument, "fp8 grouped GEMM: shard [%d, %d) of an intermediate size %d (which must be a multiple of %d, the offset of 64)", i_offset, i_offset + a.inter, i_total, kGroup);
   if (a.top_k <= 0 || a.numel < 0 || a.max_m_blocks < 0 || a.status == nullptr)
     return set_error(kStatusInvalidArgument, "fp8 grouped GEMM: bad routing sizes or null status word");
   if (a.activation != 0) return set_error(kStatusInvalidArgument, "fp8 grouped GEMM: only the silu activation is built");
@@ -431,15 +448,16 @@ int check_fp8_shapes(const GroupedGemmArgs& a) {
 
 }  // namespace
 
-int launch_quant_rows_fp8(const __nv_bfloat16* x, int rows, int cols, uint8_t* q, float* s, const int* sorted_ids,
-                          int numel, const int* num_post_pad, cudaStream_t stream) {
-  if (rows < 0 || cols <= 0 || cols % kGroup != 0)
-    return set_error(kStatusInvalidArgument, "fp8 quantisation: the row length must be a multiple of %d (got %d)", kGroup, cols);
+int launch_quant_rows_fp8(const __nv_bfloat16* x, int rows, int cols, int shift, uint8_t* q, float* s,
+                          const int* sorted_ids, int numel, const int* num_post_pad, cudaStream_t stream) {
+  if (rows < 0 || cols <= 0 || cols % 4 != 0 || shift < 0 || shift >= kGroup || shift % 4 != 0 ||
+      (sorted_ids == nullptr && (cols % kGroup != 0 || shift != 0)))
+    return set_error(kStatusInvalidArgument, "fp8 quantisation: unsupported row length %d / shift %d", cols, shift);
   if (rows == 0) return kStatusOk;
   if (sorted_ids != nullptr) {
     if (rows % BM != 0) return set_error(kStatusInvalidArgument, "fp8 quantisation of permuted rows: %d rows is not a multiple of %d", rows, BM);
     if (int st = check_cuda(launch_pdl(quant_permuted_rows_fp8_kernel, dim3(static_cast<unsigned>(rows / BM), numel > 4096 ? 8u : 1u), dim3(256), 0,
-                                       stream, x, cols, q, s, sorted_ids, numel, num_post_pad),
+                                       stream, x, cols, shift, q, s, sorted_ids, numel, num_post_pad),
                             "quant_permuted_rows_fp8 launch"))
       return st;
     count_launches(1);
@@ -455,8 +473,8 @@ int launch_quant_rows_fp8(const __nv_bfloat16* x, int rows, int cols, uint8_t* q
 }
 
 int launch_grouped_gemm1_fp8(const GroupedGemmArgs& a, const uint8_t* x_q, const float* x_s, const uint8_t* w13_q,
-                             const float* w13_s, __nv_bfloat16* h_sorted, cudaStream_t stream) {
-  if (int st = check_fp8_shapes(a)) return st;
+                             const float* w13_s, int i_offset, int i_total, __nv_bfloat16* h_sorted, cudaStream_t stream) {
+  if (int st = check_fp8_shapes(a, i_offset, i_total)) return st;
   if (a.numel == 0 || a.max_m_blocks == 0) return kStatusOk;
   if (int st = ensure_smem_attr_f8<1>()) return st;
   CUtensorMap map_b;
@@ -465,7 +483,10 @@ int launch_grouped_gemm1_fp8(const GroupedGemmArgs& a, const uint8_t* x_q, const
   if (int st = make_map(&map_b, w13_q, 3, dims, box, 1)) return st;
   ParamsF8 p{};
   p.sorted_ids = a.sorted_ids; p.expert_ids = a.expert_ids; p.num_post_pad = a.num_post_pad;
-  p.a_q = x_q; p.a_s = x_s; p.w_s = w13_s; p.w_s_rows = (2 * a.inter + kGroup - 1) / kGroup;
+  p.a_q = x_q; p.a_s = x_s; p.w_s = w13_s;
+  // scales of the unsharded [E, 2 I, H] weight: gate rows of this shard start at i_offset, up rows at I + i_offset
+  p.w_s_rows = 2 * i_total / kGroup; p.w_s_ld = a.hidden / kGroup; p.a_s_ld = a.hidden / kGroup;
+  p.num_kb = a.hidden / kGroup; p.k_shift = 0; p.w_kb_off = 0; p.row_blk0 = i_offset; p.row_blk1 = i_total + i_offset;
   p.numel = a.numel; p.top_k = a.top_k; p.K = a.hidden;
   p.tile_cols = 64; p.n_tiles = a.inter / 64; p.out_cols = a.inter; p.inter = a.inter;
   p.out = h_sorted; p.out_ld = a.inter; p.topk_w = nullptr; p.status = a.status;
@@ -479,8 +500,9 @@ int launch_grouped_gemm1_fp8(const GroupedGemmArgs& a, const uint8_t* x_q, const
 }
 
 int launch_grouped_gemm2_fp8(const GroupedGemmArgs& a, const uint8_t* h_q, const float* h_s, const uint8_t* w2_q,
-                             const float* w2_s, const float* topk_w, __nv_bfloat16* c3, cudaStream_t stream) {
-  if (int st = check_fp8_shapes(a)) return st;
+                             const float* w2_s, int i_offset, int i_total, const float* topk_w, __nv_bfloat16* c3,
+                             cudaStream_t stream) {
+  if (int st = check_fp8_shapes(a, i_offset, i_total)) return st;
   if (a.numel == 0 || a.max_m_blocks == 0) return kStatusOk;
   if (int st = ensure_smem_attr_f8<2>()) return st;
   CUtensorMap map_b;
@@ -489,7 +511,12 @@ int launch_grouped_gemm2_fp8(const GroupedGemmArgs& a, const uint8_t* h_q, const
   if (int st = make_map(&map_b, w2_q, 3, dims, box, 1)) return st;
   ParamsF8 p{};
   p.sorted_ids = a.sorted_ids; p.expert_ids = a.expert_ids; p.num_post_pad = a.num_post_pad;
-  p.a_q = h_q; p.a_s = h_s; p.w_s = w2_s; p.w_s_rows = (a.hidden + kGroup - 1) / kGroup;
+  p.a_q = h_q; p.a_s = h_s; p.w_s = w2_s;
+  // K = this rank's slice [i_offset, i_offset + inter) of I: K blocks follow the scale blocks of the unsharded weight
+  p.k_shift = i_offset % kGroup;
+  p.num_kb = (p.k_shift + a.inter + kGroup - 1) / kGroup;
+  p.w_kb_off = i_offset / kGroup;
+  p.w_s_rows = a.hidden / kGroup; p.w_s_ld = i_total / kGroup; p.a_s_ld = p.num_kb; p.row_blk0 = 0; p.row_blk1 = 0;
   p.numel = a.numel; p.top_k = a.top_k; p.K = a.inter;
   p.tile_cols = 128; p.n_tiles = a.hidden / 128; p.out_cols = a.hidden; p.inter = 0;
   p.out = c3; p.out_ld = a.hidden; p.topk_w = topk_w; p.status = a.status;

@@ -90,14 +90,18 @@ int launch_add_rms_norm_router(const __nv_bfloat16* input, __nv_bfloat16* residu
                                void* workspace, size_t workspace_bytes, int* status_word, cudaStream_t stream);
 
 // ---- grouped_gemm_fp8.cu (e4m3 weights with 128 x 128 block scales, activations quantised per row and 128 columns)
-// q[r, c] = e4m3(x[r, c] / s[r, c / 128]), s = max(|x| over the group, 1e-10) / 448. With sorted_ids given, rows that are
-// padding of the permutation (or lie beyond *num_post_pad) are skipped.
-int launch_quant_rows_fp8(const __nv_bfloat16* x, int rows, int cols, uint8_t* q, float* s, const int* sorted_ids,
-                          int numel, const int* num_post_pad, cudaStream_t stream);
+// q[r, c] = e4m3(x[r, c] / s[r, g]), s = max(|x| over the group, 1e-10) / 448; group g = columns
+// [128 g - shift, 128 (g + 1) - shift) cut to the row. With sorted_ids given, rows that are padding of the
+// permutation (or lie beyond *num_post_pad) are skipped; shift != 0 needs sorted_ids.
+int launch_quant_rows_fp8(const __nv_bfloat16* x, int rows, int cols, int shift, uint8_t* q, float* s,
+                          const int* sorted_ids, int numel, const int* num_post_pad, cudaStream_t stream);
+// The weight scales are those of the UNSHARDED tensors ([E, 2 I/128, H/128] and [E, H/128, I/128]); the rank holds
+// the slice [i_offset, i_offset + a.inter) of the intermediate dimension I = i_total.
 int launch_grouped_gemm1_fp8(const GroupedGemmArgs& a, const uint8_t* x_q, const float* x_s, const uint8_t* w13_q,
-                             const float* w13_s, __nv_bfloat16* h_sorted, cudaStream_t stream);
+                             const float* w13_s, int i_offset, int i_total, __nv_bfloat16* h_sorted, cudaStream_t stream);
 int launch_grouped_gemm2_fp8(const GroupedGemmArgs& a, const uint8_t* h_q, const float* h_s, const uint8_t* w2_q,
-                             const float* w2_s, const float* topk_w, __nv_bfloat16* c3, cudaStream_t stream);
+                             const float* w2_s, int i_offset, int i_total, const float* topk_w, __nv_bfloat16* c3,
+                             cudaStream_t stream);
 // Tensor map of a dense bf16 (elem_bytes 2) or byte (elem_bytes 1) tensor, 128-byte swizzle; dims/box innermost first.
 int make_map(CUtensorMap* map, const void* base, int rank, const uint64_t* dims, const uint32_t* box, int elem_bytes);
 // Token blocks the permutation is expected to produce, and the share of SM-time a round-robin tile list keeps busy.

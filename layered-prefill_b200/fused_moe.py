@@ -167,7 +167,8 @@ def fused_moe_forward_reduce_norm(hidden_states: torch.Tensor, router_logits: to
 
 def _fused_experts_fp8(hidden_states, w1, w2, topk_weights, topk_ids, inplace, activation, w1_scale, w2_scale,
                        block_shape, w1_bias, w2_bias, a1_scale, a2_scale, w1_zp, w2_zp, expert_map,
-                       apply_router_weight_on_input, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                       apply_router_weight_on_input, out: Optional[torch.Tensor] = None,
+                       intermediate_offset: int = 0, intermediate_size: Optional[int] = None) -> torch.Tensor:
     """w8a8 e4m3: weights [E, 2I, H] / [E, H, I] with fp32 scales per 128 x 128 block, activations quantised per
     token and 128 columns inside the library (dynamic, so a1_scale / a2_scale stay None)."""
     if not hidden_states.is_cuda:
@@ -189,12 +190,15 @@ def _fused_experts_fp8(hidden_states, w1, w2, topk_weights, topk_ids, inplace, a
     E, two_i, _ = w1.shape
     inter = two_i // 2
     assert w1.shape == (E, 2 * inter, H) and w2.shape == (E, H, inter)
-    if H % 128 or inter % 128:
-        raise ValueError(f"fp8 path needs H and I to be multiples of 128 (H={H}, I={inter})")
+    i_total = inter if intermediate_size is None else int(intermediate_size)
+    i_off = int(intermediate_offset)
+    if H % 128 or i_total % 128 or inter % 64 or i_off % 64 or i_off < 0 or i_off + inter > i_total:
+        raise ValueError(f"fp8 path needs H and I to be multiples of 128 and a rank's slice of I to start and end "
+                         f"on multiples of 64 (H={H}, I={i_total}, slice [{i_off}, {i_off + inter}))")
     s1 = w1_scale.to(torch.float32).contiguous()
     s2 = w2_scale.to(torch.float32).contiguous()
-    assert s1.shape == (E, 2 * inter // 128, H // 128), f"w1_scale shape {tuple(s1.shape)}"
-    assert s2.shape == (E, H // 128, inter // 128), f"w2_scale shape {tuple(s2.shape)}"
+    assert s1.shape == (E, 2 * i_total // 128, H // 128), f"w1_scale shape {tuple(s1.shape)}"
+    assert s2.shape == (E, H // 128, i_total // 128), f"w2_scale shape {tuple(s2.shape)}"
     k = topk_ids.size(1)
     if out is None:
         out = hidden_states if inplace else torch.empty_like(hidden_states)
@@ -209,11 +213,24 @@ def _fused_experts_fp8(hidden_states, w1, w2, topk_weights, topk_ids, inplace, a
     import ctypes
     fptr = ctypes.POINTER(ctypes.c_float)
     with torch.cuda.device(dev):
-        check(lib.moe_b200_fused_experts_fp8(
+        check(lib.moe_b200_fused_experts_fp8_tp(
             hidden_states.data_ptr(), w1.data_ptr(), ctypes.cast(s1.data_ptr(), fptr), w2.data_ptr(),
-            ctypes.cast(s2.data_ptr(), fptr), tw.data_ptr(), ti.data_ptr(), out.data_ptr(), T, E, k, H, inter,
-            ws.data_ptr(), ws.numel(), ops.status_word(dev).data_ptr(), torch.cuda.current_stream().cuda_stream))
+            ctypes.cast(s2.data_ptr(), fptr), tw.data_ptr(), ti.data_ptr(), out.data_ptr(), T, E, k, H, inter, i_off,
+            i_total, ws.data_ptr(), ws.numel(), ops.status_word(dev).data_ptr(),
+            torch.cuda.current_stream().cuda_stream))
     return out
+
+
+def fused_experts_fp8_shard(hidden_states: torch.Tensor, w13_q: torch.Tensor, w13_scale: torch.Tensor,
+                            w2_q: torch.Tensor, w2_scale: torch.Tensor, topk_weights: torch.Tensor,
+                            topk_ids: torch.Tensor, intermediate_offset: int, intermediate_size: int,
+                            out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """One tensor-parallel rank of the fp8 experts: w13_q [E, 2*Ip, H] / w2_q [E, H, Ip] hold the slice
+    [intermediate_offset, intermediate_offset + Ip) of the intermediate dimension (sharded as FusedMoE.weight_loader
+    shards bf16 weights), the scales are those of the unsharded weights. Returns this rank's partial sum."""
+    return _fused_experts_fp8(hidden_states, w13_q, w2_q, topk_weights, topk_ids, False, "silu", w13_scale, w2_scale,
+                              [128, 128], None, None, None, None, None, None, None, False, out=out,
+                              intermediate_offset=intermediate_offset, intermediate_size=intermediate_size)
 
 
 def pre_moe(hidden_states: torch.Tensor, residual: torch.Tensor, norm_weight: torch.Tensor, eps: float,

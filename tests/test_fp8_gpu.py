@@ -147,3 +147,41 @@ def test_fp8_block_with_the_steps_in_front_replays_from_a_cuda_graph():
         # comparison uses the tolerance of the dequantised path rather than the emulation's
         assert O.rel_l2(out.cpu(), want) <= REL_L2_DEQUANT
     _status_ok()
+
+
+@pytest.mark.parametrize("T,H,E,k,I,tp,ranks", [
+    (40, 256, 4, 2, 384, 2, (0, 1)),          # I/tp = 192: rank 1's slice starts in the middle of a scale block
+    (130, 256, 8, 2, 768, 4, (0, 1, 2, 3)),   # slices [0,192) [192,384) [384,576) [576,768): shifts 0, 64, 0, 64
+    (64, 512, 4, 4, 1536, 8, (0, 1, 6, 7)),   # the benchmark's 235B intermediate size at TP = 8
+    (33, 256, 4, 2, 512, 2, (0, 1)),          # I/tp = 256: aligned slices take the same path with shift 0
+])
+def test_fp8_tensor_parallel_shards_use_the_unsharded_scale_blocks(T, H, E, k, I, tp, ranks):
+    """One rank of a tensor-parallel fp8 layer on one GPU: weights sliced over I the way weight_loader slices them,
+    scales of the unsharded tensors, the rank's partial sum against the CPU emulation of the same rank."""
+    from layered_prefill_b200 import fused_moe
+    g = torch.Generator().manual_seed(T + I + tp)
+    x = torch.randn(T, H, generator=g).to(torch.bfloat16)
+    w13 = (torch.randn(E, 2 * I, H, generator=g) * 0.03).to(torch.bfloat16)
+    w2 = (torch.randn(E, H, I, generator=g) * 0.03).to(torch.bfloat16)
+    q13, s13 = O.quant_weight_block_fp8(w13)
+    q2, s2 = O.quant_weight_block_fp8(w2)
+    tw, ti, _ = O.fused_topk(x, torch.randn(T, E, generator=g), k, True)
+    d = _dev()
+    ip = I // tp
+    parts = {}
+    for r in ranks:
+        lo, hi = r * ip, (r + 1) * ip
+        b13, b2 = q13.view(torch.uint8), q2.view(torch.uint8)
+        q13r = torch.cat([b13[:, lo:hi], b13[:, I + lo:I + hi]], dim=1).contiguous().view(torch.float8_e4m3fn)
+        q2r = b2[:, :, lo:hi].contiguous().view(torch.float8_e4m3fn)
+        want = O.fused_experts_fp8(x, q13r, s13, q2r, s2, tw, ti, i_offset=lo, i_total=I)
+        got = fused_moe.fused_experts_fp8_shard(x.to(d), q13r.to(d), s13.to(d), q2r.to(d), s2.to(d), tw.to(d), ti.to(d),
+                                                lo, I).cpu()
+        _status_ok()
+        assert torch.isfinite(got.float()).all()
+        assert O.rel_l2(got, want) <= REL_L2_EMULATION, (r, O.rel_l2(got, want), O.max_abs(got, want))
+        parts[r] = got
+    if len(ranks) == tp:  # all ranks present: their sum is the layer's output, close to the unsharded emulation
+        total = O.all_reduce([parts[r] for r in range(tp)])
+        full = O.fused_experts_fp8(x, q13, s13, q2, s2, tw, ti)
+        assert O.rel_l2(total, full) <= 3e-2   # a slice that splits a scale block quantises its halves separately
