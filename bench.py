@@ -314,7 +314,6 @@ def main():
             del w13_full, w2_full
     torch.cuda.synchronize()
     out = torch.empty_like(x)
-    fp8_partial = torch.empty_like(x) if (args.fp8 and tp > 1) else None
 
     def block(i, xin, lgin, dst):
         if args.fp8:
@@ -322,8 +321,7 @@ def main():
             if tp == 1:
                 return fused_moe.fused_moe_forward_fp8(xin, lgin, q13, s13, q2, s2, wl.top_k, True, out=dst)
             tw_, ti_, _ = fused_moe.fused_topk(xin, lgin, wl.top_k, True)
-            part = fused_moe.fused_experts_fp8_shard(xin, q13, s13, q2, s2, tw_, ti_, rank * ip, wl.I, out=fp8_partial)
-            return comm.all_reduce(part, out=dst)
+            return fused_moe.fused_experts_fp8_shard(xin, q13, s13, q2, s2, tw_, ti_, rank * ip, wl.I, out=dst, comm=comm)
         w13, w2 = sets[i % n_sets]
         return fused_moe.fused_moe_forward(xin, lgin, w13, w2, wl.top_k, True, "silu", inplace=False, comm=comm,
                                            out=dst)
@@ -705,8 +703,7 @@ def main():
                        "tensor_parallel": tp, "I_per_rank": ip,
                        "launch": "cuda graph replay per step" if use_graph else "eager launches",
                        "l2": f"weights rotate over {n_sets} distinct copies ({n_sets * 3 * wl.E * wl.H * ip * (1 if args.fp8 else 2) / 1e6:.0f} MB per rank) so no step finds them in L2",
-                       "all_reduce": ("none (1 GPU)" if world == 1 else "k-slot sum kernel, then peer-memory all-reduce" if args.fp8
-                                      else "fused k-slot sum + peer-memory all-reduce")},
+                       "all_reduce": "fused k-slot sum + peer-memory all-reduce" if world > 1 else "none (1 GPU)"},
             "us_per_layer": ms_per_step * 1e3, "tokens_per_s": wl.T / (ms_per_step * 1e-3),
             "roofline": roofline, "block": block_stats, "cpu_baseline": cpu_baseline, "e2e": e2e,
             "gpu_launches": launches, "clocks": clocks,

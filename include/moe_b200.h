@@ -177,6 +177,13 @@ int moe_b200_fused_experts_fp8_tp(const void* x, const void* w13_q, const float*
                                   const float* w2_scale, const float* topk_weights, const int32_t* topk_ids, void* out,
                                   int T, int E, int top_k, int H, int I, int i_offset, int i_total, void* workspace,
                                   size_t workspace_bytes, int32_t* status_word, void* stream);
+/* The same with the k-slot sum fused into the peer-memory all-reduce (as moe_b200_fused_moe_forward_tp does for bf16):
+ * out = the layer's output on every rank. */
+int moe_b200_fused_experts_fp8_tp_reduce(const void* x, const void* w13_q, const float* w13_scale, const void* w2_q,
+                                         const float* w2_scale, const float* topk_weights, const int32_t* topk_ids,
+                                         void* out, int T, int E, int top_k, int H, int I, int i_offset, int i_total,
+                                         void* workspace, size_t workspace_bytes, int64_t ar_handle, int64_t reg_buffer,
+                                         int64_t reg_buffer_bytes, int ar_algo, int32_t* status_word, void* stream);
 /* q[r, c] = e4m3(x[r, c] / s[r, c/128]), s[r, g] = max(|x[r, 128g .. 128g+127]|, 1e-10) / 448; x bf16 [rows, cols],
  * cols % 128 == 0. The activation quantisation the call above applies (exposed for tests and for callers
  * that keep quantised activations). */

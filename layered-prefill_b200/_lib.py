@@ -68,6 +68,7 @@ SIGNATURES = {
     "moe_b200_fused_experts_fp8_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int, c_int]),
     "moe_b200_fused_experts_fp8": (c_int, [c_void_p, c_void_p, POINTER(c_float), c_void_p, POINTER(c_float), c_void_p, c_void_p, c_void_p] + [c_int] * 5 + [c_void_p, c_size_t, c_void_p, c_void_p]),
     "moe_b200_fused_experts_fp8_tp": (c_int, [c_void_p, c_void_p, POINTER(c_float), c_void_p, POINTER(c_float), c_void_p, c_void_p, c_void_p] + [c_int] * 7 + [c_void_p, c_size_t, c_void_p, c_void_p]),
+    "moe_b200_fused_experts_fp8_tp_reduce": (c_int, [c_void_p, c_void_p, POINTER(c_float), c_void_p, POINTER(c_float), c_void_p, c_void_p, c_void_p] + [c_int] * 7 + [c_void_p, c_size_t, c_int64, c_int64, c_int64, c_int, c_void_p, c_void_p]),
     "moe_b200_quant_fp8_per_token_group": (c_int, [c_void_p, c_int, c_int, c_void_p, POINTER(c_float), c_void_p]),
     "moe_b200_fused_moe_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int, c_int]),
     "moe_b200_fused_moe_forward": (c_int, [c_void_p, c_void_p, c_int] + [c_void_p] * 7 + [c_int] * 7 + [c_void_p, c_size_t, c_void_p, c_void_p]),

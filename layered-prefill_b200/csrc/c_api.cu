@@ -352,21 +352,21 @@ size_t moe_b200_fused_experts_fp8_workspace_bytes(int T, int E, int top_k, int H
   return carve_fp8(nullptr, T, E, top_k, H, I).total;
 }
 
-int moe_b200_fused_experts_fp8_tp(const void* x, const void* w13_q, const float* w13_scale, const void* w2_q,
-                                  const float* w2_scale, const float* topk_weights, const int32_t* topk_ids, void* out,
-                                  int T, int E, int top_k, int H, int I, int i_offset, int i_total, void* workspace,
-                                  size_t workspace_bytes, int32_t* status_word, void* stream) {
+// Everything of the fp8 experts up to (not including) the k-slot sum; returns the C3 slot tensor in the workspace.
+static int run_experts_fp8_until_c3(const void* x, const void* w13_q, const float* w13_scale, const void* w2_q,
+                                    const float* w2_scale, const float* topk_weights, const int32_t* topk_ids, int T, int E,
+                                    int top_k, int H, int I, int i_offset, int i_total, void* workspace,
+                                    size_t workspace_bytes, int32_t* status_word, cudaStream_t s,
+                                    const __nv_bfloat16** c3_out) {
   if (int st = check_block_shapes(T, E, top_k, H, I)) return st;
   if (H % 128 != 0 || I % 64 != 0 || i_total % 128 != 0 || i_offset % 64 != 0 || i_offset < 0 || i_offset + I > i_total)
     return set_error(kStatusInvalidArgument, "fused_experts_fp8: H must be a multiple of 128, the intermediate size %d of 128, this rank's slice [%d, %d) of 64 (H=%d)", i_total, i_offset, i_offset + I, H);
-  if (T == 0) return kStatusOk;
   if (x == nullptr || w13_q == nullptr || w13_scale == nullptr || w2_q == nullptr || w2_scale == nullptr ||
-      topk_weights == nullptr || topk_ids == nullptr || out == nullptr || status_word == nullptr)
+      topk_weights == nullptr || topk_ids == nullptr || status_word == nullptr)
     return set_error(kStatusInvalidArgument, "fused_experts_fp8: null pointer");
   const size_t need = moe_b200_fused_experts_fp8_workspace_bytes(T, E, top_k, H, I);
   if (workspace == nullptr || workspace_bytes < need)
     return set_error(kStatusWorkspaceTooSmall, "fused_experts_fp8: workspace of %zu bytes needed, %zu given", need, workspace_bytes);
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
   const Fp8Workspace w = carve_fp8(workspace, T, E, top_k, H, I);
   const PermSizes ps = perm_sizes(T, E, top_k);
   if (int st = launch_quant_rows_fp8(static_cast<const __nv_bfloat16*>(x), T, H, 0, w.x_q, w.x_s, nullptr, 0, nullptr, s)) return st;
@@ -386,7 +386,37 @@ int moe_b200_fused_experts_fp8_tp(const void* x, const void* w13_q, const float*
   if (int st = launch_grouped_gemm2_fp8(a, w.h_q, w.h_s, static_cast<const uint8_t*>(w2_q), w2_scale, i_offset, i_total,
                                         topk_weights, w.base.c3, s))
     return st;
-  return launch_moe_sum(w.base.c3, static_cast<__nv_bfloat16*>(out), T, top_k, H, s);
+  *c3_out = w.base.c3;
+  return kStatusOk;
+}
+
+int moe_b200_fused_experts_fp8_tp(const void* x, const void* w13_q, const float* w13_scale, const void* w2_q,
+                                  const float* w2_scale, const float* topk_weights, const int32_t* topk_ids, void* out,
+                                  int T, int E, int top_k, int H, int I, int i_offset, int i_total, void* workspace,
+                                  size_t workspace_bytes, int32_t* status_word, void* stream) {
+  if (T == 0) return check_block_shapes(T, E, top_k, H, I);
+  if (out == nullptr) return set_error(kStatusInvalidArgument, "fused_experts_fp8: null pointer");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const __nv_bfloat16* c3 = nullptr;
+  if (int st = run_experts_fp8_until_c3(x, w13_q, w13_scale, w2_q, w2_scale, topk_weights, topk_ids, T, E, top_k, H, I,
+                                        i_offset, i_total, workspace, workspace_bytes, status_word, s, &c3))
+    return st;
+  return launch_moe_sum(c3, static_cast<__nv_bfloat16*>(out), T, top_k, H, s);
+}
+
+int moe_b200_fused_experts_fp8_tp_reduce(const void* x, const void* w13_q, const float* w13_scale, const void* w2_q,
+                                         const float* w2_scale, const float* topk_weights, const int32_t* topk_ids,
+                                         void* out, int T, int E, int top_k, int H, int I, int i_offset, int i_total,
+                                         void* workspace, size_t workspace_bytes, int64_t ar_handle, int64_t reg_buffer,
+                                         int64_t reg_buffer_bytes, int ar_algo, int32_t* status_word, void* stream) {
+  if (T == 0) return check_block_shapes(T, E, top_k, H, I);
+  if (out == nullptr || ar_handle == 0) return set_error(kStatusInvalidArgument, "fused_experts_fp8_tp_reduce: null pointer or no communicator");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const __nv_bfloat16* c3 = nullptr;
+  if (int st = run_experts_fp8_until_c3(x, w13_q, w13_scale, w2_q, w2_scale, topk_weights, topk_ids, T, E, top_k, H, I,
+                                        i_offset, i_total, workspace, workspace_bytes, status_word, s, &c3))
+    return st;
+  return ar_moe_sum_all_reduce_impl(ar_handle, c3, out, T, top_k, H, reg_buffer, reg_buffer_bytes, ar_algo, status_word, s);
 }
 
 int moe_b200_fused_experts_fp8(const void* x, const void* w13_q, const float* w13_scale, const void* w2_q,

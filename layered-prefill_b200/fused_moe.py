@@ -168,7 +168,7 @@ def fused_moe_forward_reduce_norm(hidden_states: torch.Tensor, router_logits: to
 def _fused_experts_fp8(hidden_states, w1, w2, topk_weights, topk_ids, inplace, activation, w1_scale, w2_scale,
                        block_shape, w1_bias, w2_bias, a1_scale, a2_scale, w1_zp, w2_zp, expert_map,
                        apply_router_weight_on_input, out: Optional[torch.Tensor] = None,
-                       intermediate_offset: int = 0, intermediate_size: Optional[int] = None) -> torch.Tensor:
+                       intermediate_offset: int = 0, intermediate_size: Optional[int] = None, comm=None) -> torch.Tensor:
     """w8a8 e4m3: weights [E, 2I, H] / [E, H, I] with fp32 scales per 128 x 128 block, activations quantised per
     token and 128 columns inside the library (dynamic, so a1_scale / a2_scale stay None)."""
     if not hidden_states.is_cuda:
@@ -213,24 +213,32 @@ def _fused_experts_fp8(hidden_states, w1, w2, topk_weights, topk_ids, inplace, a
     import ctypes
     fptr = ctypes.POINTER(ctypes.c_float)
     with torch.cuda.device(dev):
-        check(lib.moe_b200_fused_experts_fp8_tp(
-            hidden_states.data_ptr(), w1.data_ptr(), ctypes.cast(s1.data_ptr(), fptr), w2.data_ptr(),
-            ctypes.cast(s2.data_ptr(), fptr), tw.data_ptr(), ti.data_ptr(), out.data_ptr(), T, E, k, H, inter, i_off,
-            i_total, ws.data_ptr(), ws.numel(), ops.status_word(dev).data_ptr(),
-            torch.cuda.current_stream().cuda_stream))
+        if comm is not None and not comm.disabled and comm.world_size > 1 and T * H * 2 <= comm.max_size:
+            check(lib.moe_b200_fused_experts_fp8_tp_reduce(
+                hidden_states.data_ptr(), w1.data_ptr(), ctypes.cast(s1.data_ptr(), fptr), w2.data_ptr(),
+                ctypes.cast(s2.data_ptr(), fptr), tw.data_ptr(), ti.data_ptr(), out.data_ptr(), T, E, k, H, inter, i_off,
+                i_total, ws.data_ptr(), ws.numel(), comm._ptr, comm.buffer_ptrs[comm.rank], comm.max_size, 0,
+                ops.status_word(dev).data_ptr(), torch.cuda.current_stream().cuda_stream))
+        else:
+            check(lib.moe_b200_fused_experts_fp8_tp(
+                hidden_states.data_ptr(), w1.data_ptr(), ctypes.cast(s1.data_ptr(), fptr), w2.data_ptr(),
+                ctypes.cast(s2.data_ptr(), fptr), tw.data_ptr(), ti.data_ptr(), out.data_ptr(), T, E, k, H, inter, i_off,
+                i_total, ws.data_ptr(), ws.numel(), ops.status_word(dev).data_ptr(),
+                torch.cuda.current_stream().cuda_stream))
     return out
 
 
 def fused_experts_fp8_shard(hidden_states: torch.Tensor, w13_q: torch.Tensor, w13_scale: torch.Tensor,
                             w2_q: torch.Tensor, w2_scale: torch.Tensor, topk_weights: torch.Tensor,
                             topk_ids: torch.Tensor, intermediate_offset: int, intermediate_size: int,
-                            out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                            out: Optional[torch.Tensor] = None, comm=None) -> torch.Tensor:
     """One tensor-parallel rank of the fp8 experts: w13_q [E, 2*Ip, H] / w2_q [E, H, Ip] hold the slice
     [intermediate_offset, intermediate_offset + Ip) of the intermediate dimension (sharded as FusedMoE.weight_loader
-    shards bf16 weights), the scales are those of the unsharded weights. Returns this rank's partial sum."""
+    shards bf16 weights), the scales are those of the unsharded weights. Returns this rank's partial sum, or, with
+    `comm` (an initialised CustomAllreduce), the layer's output: the k-slot sum then runs inside the all-reduce."""
     return _fused_experts_fp8(hidden_states, w13_q, w2_q, topk_weights, topk_ids, False, "silu", w13_scale, w2_scale,
                               [128, 128], None, None, None, None, None, None, None, False, out=out,
-                              intermediate_offset=intermediate_offset, intermediate_size=intermediate_size)
+                              intermediate_offset=intermediate_offset, intermediate_size=intermediate_size, comm=comm)
 
 
 def pre_moe(hidden_states: torch.Tensor, residual: torch.Tensor, norm_weight: torch.Tensor, eps: float,

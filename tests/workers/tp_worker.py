@@ -163,6 +163,36 @@ def main():
     assert torch.equal(res_a, res_b) and torch.equal(norm_a, norm_b)
     assert ops.read_status(dev) == 0
 
+    # ---- 6. fp8 experts, tensor parallel with I/tp = 192 (slices split the 128-wide scale blocks), k-slot sum fused
+    # with the all-reduce: against the all-reduced per-rank CPU emulations
+    g = torch.Generator().manual_seed(91)
+    T, H, E, k, I = 48, 256, 4, 2, 192 * world
+    x = torch.randn(T, H, generator=g).to(torch.bfloat16)
+    w13 = (torch.randn(E, 2 * I, H, generator=g) * 0.03).to(torch.bfloat16)
+    w2 = (torch.randn(E, H, I, generator=g) * 0.03).to(torch.bfloat16)
+    q13, s13 = O.quant_weight_block_fp8(w13)
+    q2, s2 = O.quant_weight_block_fp8(w2)
+    tw, ti, _ = O.fused_topk(x, torch.randn(T, E, generator=g), k, True)
+    ip = I // world
+    b13, b2 = q13.view(torch.uint8), q2.view(torch.uint8)
+
+    def shard(r):
+        lo, hi = r * ip, (r + 1) * ip
+        return (torch.cat([b13[:, lo:hi], b13[:, I + lo:I + hi]], dim=1).contiguous().view(torch.float8_e4m3fn),
+                b2[:, :, lo:hi].contiguous().view(torch.float8_e4m3fn))
+
+    want = O.all_reduce([O.fused_experts_fp8(x, *[t for t in (shard(r)[0], s13, shard(r)[1], s2)], tw, ti,
+                                             i_offset=r * ip, i_total=I) for r in range(world)])
+    q13r, q2r = shard(rank)
+    got = fused_moe.fused_experts_fp8_shard(x.to(dev), q13r.to(dev), s13.to(dev), q2r.to(dev), s2.to(dev), tw.to(dev),
+                                            ti.to(dev), rank * ip, I, comm=comm)
+    torch.cuda.synchronize()
+    assert ops.read_status(dev) == 0
+    assert O.rel_l2(got.cpu(), want) <= 5e-3, O.rel_l2(got.cpu(), want)
+    gathered = [torch.empty_like(got) for _ in range(world)]
+    dist.all_gather(gathered, got)
+    assert all(torch.equal(gathered[0], t) for t in gathered)
+
     dist.barrier()
     comm.close()
     dist.destroy_process_group()
