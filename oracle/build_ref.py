@@ -1,10 +1,10 @@
 """TEST INFRASTRUCTURE: compiles the reference's own CUDA ops, from the sources where they lie in the
 mounted reference tree, into oracle/_ref/nanovllm_ref_ops.so (a pybind11 module with the reference's
 `nanovllm.ops` functions). Nothing is copied into this repository; oracle/_ref/ is git-ignored and
-only the built binary travels to the GPU box, where tests use it as a second checker next to the CPU
-oracle (`load_reference_ops()` returns None when it is absent).
+only the built binary goes along to machines without the reference tree, where tests use it as a second checker
+next to the CPU oracle (`load_reference_ops()` returns None when it is absent).
 
-    python oracle/build_ref.py [/root/reference]
+    python oracle/build_ref.py [<path of the reference tree>]
 
 The reference builds this extension with setup.py (one CUDAExtension, -O3 -std=c++17, no fast-math,
 setup.py:46-47,76-93); this recipe compiles the same eight sources with the same flags, for sm_100a.

@@ -1,7 +1,7 @@
 """Generates tests/golden/reference_helpers.npz from the reference's own CPU-runnable helpers.
 
-Run in the build container, where the reference tree is mounted:
-    python tests/golden/make_golden.py /root/reference
+Run where the reference tree is mounted:
+    python tests/golden/make_golden.py <path of the reference tree>
 It loads nanovllm/layers/for_moe/moe_easy_kernel.py by path (importing the nanovllm package itself
 needs modules that are not installed) and records inputs and outputs of topk_softmax, silu_and_mul,
 moe_sum and swigluoai on small seeded tensors. The tests compare the CPU oracle with these vectors;
