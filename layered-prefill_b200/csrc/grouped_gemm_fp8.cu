@@ -42,10 +42,11 @@ constexpr int kBarrierBytes = 1024;
 constexpr int kSmemBytes = kBarrierBytes + 1024 /*alignment slack*/ + kStages * kStageBytes;
 
 constexpr int kWarpTma = 0;
-constexpr int kWarpMma = 1;
-constexpr int kWarpPromote0 = 2;  // 8 warps
-constexpr int kWarpGather0 = 10;  // 4 warps
-constexpr int kThreads = 448;
+constexpr int kWarpMma = 1;       // 2 warps: issuer i takes the K blocks j with j % 2 == i
+constexpr int kMmaIssuers = 2;
+constexpr int kWarpPromote0 = 4;  // 8 warps (starting at a multiple of 4: a warp reads TMEM lane quarter warp % 4)
+constexpr int kWarpGather0 = 12;  // 4 warps
+constexpr int kThreads = 512;
 
 struct ParamsF8 {
   const int* sorted_ids;
@@ -157,14 +158,21 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_b, const Params
       }
     }
     __syncwarp();
-  } else if (warp == kWarpMma) {
-    // ------------------------------------------------------------------ MMA issuer: one stage = one product buffer
+  } else if (warp >= kWarpMma && warp < kWarpMma + kMmaIssuers) {
+    // ------------------------------------------------------------------ MMA issuers: one stage = one product buffer
+    // Issuing a tcgen05.mma costs its thread about 110 cycles, more than the 64 cycles an N = 128 instruction
+    // runs; the stage products are independent (nothing accumulates across K blocks in TMEM), so two threads
+    // take alternate K blocks.
     if (lane == 0) {
+      const uint32_t me = static_cast<uint32_t>(warp - kWarpMma);
       const uint32_t idesc = umma_idesc_e4m3(BM, kPartCols);
-      uint32_t s = 0, ph = 0, j = 0;
       bool ok = true;
+      uint32_t j = 0;
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
         for (int kb = 0; kb < num_kb; ++kb, ++j) {
+          if (j % kMmaIssuers != me) continue;
+          const uint32_t s = j % kStages;
+          const uint32_t ph = (j / kStages) & 1u;
           const uint32_t b = j % kPartBufs;
           const uint32_t bph = (j / kPartBufs) & 1u;
           if (!mbar_wait(&bar_part_free[b], bph ^ 1u)) {
@@ -189,10 +197,6 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_b, const Params
           umma_e4m3(d_tmem, adesc + 6, bdesc + 6, idesc, 1u);
           umma_commit(&bar_empty[s]);
           umma_commit(&bar_part_full[b]);
-          if (++s == kStages) {
-            s = 0;
-            ph ^= 1u;
-          }
         }
       }
     }
