@@ -214,3 +214,30 @@ def test_block_can_be_replayed_from_a_cuda_graph():
         want = O.moe_block(xs[i], lgs[i], w13, w2, k, True)
         assert O.rel_l2(out.cpu(), want) <= REL_L2 and O.max_abs(out.cpu(), want) <= MAX_ABS
     _check_status()
+
+
+def test_fused_experts_seeded_random_shapes():
+    """A seeded sweep over shapes the fixed cases do not list: H and I any multiple of 16, E and k free, token counts
+    around the 128-row block size."""
+    rng = torch.Generator().manual_seed(2024)
+
+    def pick(lo, hi, step=1):
+        return int(torch.randint(lo // step, hi // step + 1, (1,), generator=rng).item()) * step
+
+    for case in range(16):
+        E = pick(2, 24)
+        k = pick(1, min(E, 6))
+        H = pick(32, 640, 16)
+        I = pick(16, 320, 16)
+        T = pick(1, 400)
+        kw = {}
+        if case % 4 == 1:
+            kw = {"bias": True}
+        elif case % 4 == 2:
+            kw = {"activation": "swigluoai", "scale": 0.1}
+        elif case % 4 == 3:
+            kw = {"skew": 2.5}
+        try:
+            _run_case(T, H, E, k, I, seed=1000 + case, **kw)
+        except AssertionError as err:
+            raise AssertionError(f"case {case}: T={T} H={H} E={E} k={k} I={I} {kw}: {err}") from err

@@ -185,3 +185,21 @@ def test_fp8_tensor_parallel_shards_use_the_unsharded_scale_blocks(T, H, E, k, I
         total = O.all_reduce([parts[r] for r in range(tp)])
         full = O.fused_experts_fp8(x, q13, s13, q2, s2, tw, ti)
         assert O.rel_l2(total, full) <= 3e-2   # a slice that splits a scale block quantises its halves separately
+
+
+def test_fp8_experts_seeded_random_shapes():
+    rng = torch.Generator().manual_seed(77)
+
+    def pick(lo, hi, step=1):
+        return int(torch.randint(lo // step, hi // step + 1, (1,), generator=rng).item()) * step
+
+    for case in range(8):
+        E = pick(2, 12)
+        k = pick(1, min(E, 4))
+        H = pick(128, 640, 128)
+        I = pick(128, 512, 128)
+        T = pick(1, 300)
+        try:
+            _case(T, H, E, k, I, seed=500 + case, skew=2.0 if case % 2 else 0.0, given_scales=case % 3 == 0)
+        except AssertionError as err:
+            raise AssertionError(f"case {case}: T={T} H={H} E={E} k={k} I={I}: {err}") from err
