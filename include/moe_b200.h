@@ -254,6 +254,11 @@ int moe_b200_ar_init(const int64_t* meta_ptrs, int world_size, void* rank_data, 
 int moe_b200_ar_dispose(int64_t handle);
 /* ptrs[world_size]: one IPC-shared buffer per rank (ops.register_buffer, :115-123). */
 int moe_b200_ar_register_buffer(int64_t handle, const int64_t* ptrs);
+/* Hands the communicator a second registered buffer (same layout of arguments as register_buffer) that only the
+ * fused k-slot-sum + one-shot all-reduce uses, as two halves in alternation: that kernel then needs no closing
+ * barrier (the next call's opening barrier proves that every peer has finished the previous one). Optional; without
+ * it the fused call keeps both barriers. No reference counterpart. bytes: size of the buffer, a multiple of 32. */
+int moe_b200_ar_register_fused_buffer(int64_t handle, const int64_t* ptrs, int64_t bytes);
 /* out = sum over ranks of inp (bf16/fp16/fp32 by element_size+is_bf16), fp32 accumulation in rank
  * order, identical bits on every rank. If reg_buffer != 0 the input is first copied there
  * (ops.all_reduce, custom_all_reduce_kernels.cu:64-107). algo: 0 auto, 1 one-shot, 2 two-shot. */

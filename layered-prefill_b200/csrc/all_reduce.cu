@@ -37,10 +37,12 @@ namespace {
 constexpr int kMaxRanks = 8;
 constexpr int kMaxArBlocks = 128;
 constexpr int kArThreads = 512;
+constexpr int kFusedBlocks = 32;  // fixed grid of the barrier-saving one-shot kernel (its per-block call counters rely on it)
 
 struct alignas(128) Signal {
   uint32_t arrive[kMaxArBlocks][kMaxRanks];  // arrive[b][r]: written by block b of rank r
   uint32_t epoch[kMaxArBlocks];              // this rank's barrier count per block
+  uint32_t fused_calls[kFusedBlocks];        // this rank's count of barrier-saving one-shot calls, per block
 };
 constexpr size_t kMetaBytes = (sizeof(Signal) + 255) / 256 * 256;
 
@@ -201,6 +203,36 @@ __global__ void __launch_bounds__(kArThreads, 1) ar_oneshot_kernel(const ArParam
   peer_barrier<N>(p, false, &timed_out);
 }
 
+// k-slot sum + one-shot all-reduce with ONE barrier per call. The closing barrier of the kernel above only keeps a
+// rank from overwriting its buffer while a peer still reads it; here every rank owns two buffers (the halves of a
+// registered buffer that nothing else uses) and call n works in half n % 2. When a rank writes half n % 2 again, in
+// call n + 2, it has passed the opening barrier of call n + 1, which a peer's block reaches only after that peer's
+// call n has finished completely (kernels of a stream do not overlap past the dependency wait), so every peer is
+// done reading. The call counter lives in device memory, one copy per block, advanced by the kernel itself, so a
+// captured graph can be replayed any number of times; it stays equal across blocks and ranks because every such
+// launch has exactly kFusedBlocks blocks on every rank.
+template <int N>
+__global__ void __launch_bounds__(kArThreads, 1) ar_oneshot_sum_kernel(const ArParams p, long long half_vecs) {
+  __shared__ bool timed_out;
+  if (threadIdx.x == 0) timed_out = false;
+  grid_dependency_launch();
+  grid_dependency_wait();
+  const uint32_t call = p.self_sg->fused_calls[blockIdx.x];
+  const long long off = (call & 1u) ? half_vecs : 0;
+  const RankData rd = *p.rank_data;
+  const uint4* ptrs[N];
+#pragma unroll
+  for (int r = 0; r < N; ++r) ptrs[r] = static_cast<const uint4*>(rd.ptrs[r]) + off;
+  const long long tid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  uint4* own = const_cast<uint4*>(ptrs[p.rank]);
+  for (long long v = tid; v < p.nvec; v += stride) slot_sum_vec(p, own, v);
+  peer_barrier<N>(p, true, &timed_out);
+  uint4* out = static_cast<uint4*>(p.out);
+  for (long long v = tid; v < p.nvec; v += stride) out[v] = reduce_ranks<__nv_bfloat16, N>(ptrs, v);
+  if (threadIdx.x == 0) p.self_sg->fused_calls[blockIdx.x] = call + 1u;
+}
+
 // One-shot all-reduce that ends in the next layer's residual add + RMSNorm (what the decoder layer after the MoE
 // block does first with the reduced tensor: nanovllm/models/qwen3_moe.py:262-270, ops.add_rms_norm): a block owns
 // whole token rows, reduces a row over the ranks (fp32, rank order, bf16 rounding = the all-reduce's output), and
@@ -318,6 +350,8 @@ struct Comm {
   std::vector<void*> graph_unreg;
   std::map<IpcKey, char*> ipc_opened;
   unsigned long long wait_limit_ns = kWaitLimitNs;
+  RankData* fused_rd = nullptr;   // the double buffer of the barrier-saving one-shot kernel (registered, used by nothing else)
+  long long fused_bytes = 0;
 };
 
 typedef CUresult (*PointerGetAttributeFn)(void*, CUpointer_attribute, CUdeviceptr);
@@ -413,7 +447,25 @@ int ar_moe_sum_all_reduce_impl(int64_t handle, const void* c3, void* out, int T,
   p.rank_data = rd; p.sg = c->sg; p.self_sg = c->self_sg; p.out = out; p.rank = c->rank;
   p.nvec = bytes / 16; p.wait_limit_ns = c->wait_limit_ns; p.status = status_word;
   p.c3 = static_cast<const __nv_bfloat16*>(c3); p.top_k = k; p.hidden_vecs = H / 8;
-  return launch_ar<__nv_bfloat16>(*c, p, use_oneshot(*c, bytes, algo), stream);
+  const bool oneshot = use_oneshot(*c, bytes, algo);
+  if (oneshot && c->fused_rd != nullptr && bytes <= c->fused_bytes / 2) {
+    p.rank_data = c->fused_rd;
+    const long long half_vecs = c->fused_bytes / 2 / 16;
+#define MOE_B200_ARS_CASE(n) \
+  case n: launch_pdl(ar_oneshot_sum_kernel<n>, dim3(kFusedBlocks), dim3(kArThreads), 0, stream, p, half_vecs); break;
+    switch (c->world) {
+      MOE_B200_ARS_CASE(2)
+      MOE_B200_ARS_CASE(4)
+      MOE_B200_ARS_CASE(6)
+      MOE_B200_ARS_CASE(8)
+      default:
+        return set_error(kStatusInvalidArgument, "custom allreduce only supports num gpus in (2,4,6,8). Actual num gpus = %d", c->world);
+    }
+#undef MOE_B200_ARS_CASE
+    count_launches(1);
+    return check_launch("moe_sum_all_reduce (one barrier)");
+  }
+  return launch_ar<__nv_bfloat16>(*c, p, oneshot, stream);
 }
 
 // All-reduce (optionally with the k-slot sum in front) followed by residual add + RMSNorm. Small messages take the
@@ -541,6 +593,16 @@ int moe_b200_ar_register_buffer(int64_t handle, const int64_t* ptrs) {
   RankData* d = c->rank_data_next++;
   if (int st = check_cuda(cudaMemcpy(d, &data, sizeof(RankData), cudaMemcpyHostToDevice), "register_buffer copy")) return st;
   c->buffers[data.ptrs[c->rank]] = d;
+  return kStatusOk;
+}
+
+int moe_b200_ar_register_fused_buffer(int64_t handle, const int64_t* ptrs, int64_t bytes) {
+  Comm* c = as_comm(handle);
+  if (c == nullptr || ptrs == nullptr || bytes < 32 || bytes % 32 != 0)
+    return set_error(kStatusInvalidArgument, "register_fused_buffer: null argument or a size that is not a multiple of 32");
+  if (int st = moe_b200_ar_register_buffer(handle, ptrs)) return st;
+  c->fused_rd = c->buffers[reinterpret_cast<const void*>(static_cast<intptr_t>(ptrs[c->rank]))];
+  c->fused_bytes = bytes;
   return kStatusOk;
 }
 

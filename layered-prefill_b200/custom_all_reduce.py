@@ -24,6 +24,7 @@ from ._lib import check, lib
 
 MiB = 1024 * 1024
 DEFAULT_MAX_SIZE = 64 * MiB
+FUSED_BUFFER_BYTES = 1 * MiB  # two halves of 512 KiB = the largest one-shot message at 4 ranks
 
 
 def is_weak_contiguous(inp: torch.Tensor) -> bool:
@@ -101,6 +102,10 @@ class CustomAllreduce:
             self.rank_data = torch.empty(8 * MiB, dtype=torch.uint8, device=device)
             self._ptr = ops.init_custom_ar(self.meta_ptrs, self.rank_data, rank, fully_connected)
             ops.register_buffer(self._ptr, self.buffer_ptrs)
+            # two 512 KiB halves for the fused k-slot-sum + one-shot all-reduce (it alternates between them and
+            # so needs no closing barrier); nothing else may write this buffer
+            self.fused_ptrs = self.create_shared_buffer(FUSED_BUFFER_BYTES, group=self.gloo_group)
+            ops.register_fused_buffer(self._ptr, self.fused_ptrs, FUSED_BUFFER_BYTES)
 
     @contextmanager
     def capture(self):
@@ -185,6 +190,7 @@ class CustomAllreduce:
             self._ptr = 0
             self.free_shared_buffer(self.meta_ptrs, rank=self.rank)
             self.free_shared_buffer(self.buffer_ptrs, rank=self.rank)
+            self.free_shared_buffer(self.fused_ptrs, rank=self.rank)
             self.disabled = True
 
     def __del__(self):

@@ -198,6 +198,13 @@ def register_buffer(fa: int, ipc_ptrs: List[int]) -> None:
     check(lib.moe_b200_ar_register_buffer(fa, arr))
 
 
+def register_fused_buffer(fa: int, ipc_ptrs: List[int], nbytes: int) -> None:
+    """A second registered buffer, used only by the fused k-slot-sum + one-shot all-reduce (two halves in alternation,
+    which saves that kernel its closing barrier). No reference counterpart."""
+    arr = (ctypes.c_int64 * len(ipc_ptrs))(*ipc_ptrs)
+    check(lib.moe_b200_ar_register_fused_buffer(fa, arr, nbytes))
+
+
 _AR_DTYPES = {torch.bfloat16: 0, torch.float16: 1, torch.float32: 2}
 
 

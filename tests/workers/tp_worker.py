@@ -193,6 +193,53 @@ def main():
     dist.all_gather(gathered, got)
     assert all(torch.equal(gathered[0], t) for t in gathered)
 
+    # ---- 7. the fused k-slot-sum + one-shot all-reduce keeps no closing barrier (it alternates between two
+    # registered halves): many calls back to back without host synchronisation, ranks deliberately out of step,
+    # every result checked afterwards; then the same from a replayed CUDA graph
+    T, k, H, reps = 64, 8, 2048, 120
+    c3s = []
+    for variant in range(3):
+        per_rank = []
+        for r in range(world):
+            g = torch.Generator().manual_seed(400 + 10 * variant + r)
+            per_rank.append(torch.randn(T, k, H, generator=g).to(torch.bfloat16))
+        c3s.append(per_rank)
+    wants = [O.all_reduce([O.moe_sum(c) for c in per_rank]) for per_rank in c3s]
+    mine = [per_rank[rank].to(dev) for per_rank in c3s]
+    outs = torch.empty(reps, T, H, dtype=torch.bfloat16, device=dev)
+    stream = torch.cuda.current_stream().cuda_stream
+    dist.barrier()
+    for i in range(reps):
+        if (i + rank) % 7 == 0:
+            torch.cuda._sleep(200_000 * (1 + rank))   # this rank falls behind its peers for a while
+        check(lib.moe_b200_ar_moe_sum_all_reduce(comm._ptr, mine[i % 3].data_ptr(), outs[i].data_ptr(), T, k, H,
+                                                 comm.buffer_ptrs[rank], comm.max_size, 0,
+                                                 ops.status_word(dev).data_ptr(), stream))
+    torch.cuda.synchronize()
+    assert ops.read_status(dev) == 0
+    for i in range(reps):
+        assert torch.equal(outs[i].cpu(), wants[i % 3]), f"one-barrier all-reduce, call {i}"
+    c3_buf = mine[0].clone()
+    out_g = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            check(lib.moe_b200_ar_moe_sum_all_reduce(comm._ptr, c3_buf.data_ptr(), out_g.data_ptr(), T, k, H,
+                                                     comm.buffer_ptrs[rank], comm.max_size, 0,
+                                                     ops.status_word(dev).data_ptr(), side.cuda_stream))
+    torch.cuda.current_stream().wait_stream(side)
+    dist.barrier()
+    for i in range(9):   # the same graph replayed back to back: the half in use is chosen on the device
+        c3_buf.copy_(mine[i % 3])
+        graph.replay()
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(out_g.cpu(), wants[i % 3]), f"one-barrier all-reduce, graph replay {i}"
+        dist.barrier()
+    assert ops.read_status(dev) == 0
+
     dist.barrier()
     comm.close()
     dist.destroy_process_group()
