@@ -7,14 +7,16 @@
 // this follows the published block-quantisation scheme and is checked against a CPU emulation of it.
 //
 // Kernel: same skeleton as the bf16 kernels (grouped_gemm.cu): 128 permuted token rows per tile, weights by
-// TMA (byte tensor map, 128-byte swizzle), token rows by cp.async, one MMA thread, static tile list. What
+// TMA (byte tensor map, 128-byte swizzle), token rows by cp.async, static tile list. What
 // differs: a shared-memory stage holds 128 K elements = exactly one scale block, so the tensor core cannot
 // accumulate across stages. Each stage's product (4 tcgen05.mma kind::f8f6f4, K = 32 each) goes into one of
 // four 128-column TMEM buffers, and eight warps (two per TMEM lane quarter, 64 accumulator columns each) read it
 // back, multiply by the two scales and accumulate in registers; the same warps then run the epilogue (SiLU * up
 // with the bf16 kernels' rounding points, or x routed weight). The first purpose is the weight-streaming
 // regime, where halving the bytes halves the time; at prefill sizes the register accumulation costs about as
-// much as the tensor cores save.
+// much as the tensor cores save. On a tensor-parallel rank the K blocks and the scale indices follow the scale
+// blocks of the UNSHARDED weights (a slice of the intermediate dimension may begin or end inside a block), and two
+// threads issue the MMAs of alternate K blocks.
 #include <cuda_fp8.h>
 
 #include <cmath>
