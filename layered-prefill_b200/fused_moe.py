@@ -228,6 +228,23 @@ def _fused_experts_fp8(hidden_states, w1, w2, topk_weights, topk_ids, inplace, a
     return out
 
 
+def shard_fp8_expert_weights(w13_q: torch.Tensor, w2_q: torch.Tensor, tp_rank: int, tp_size: int):
+    """Slices e4m3 expert weights over the intermediate dimension the way FusedMoE.weight_loader slices bf16 ones
+    (nanovllm/layers/fused_moe.py:400-470): w13 [E, 2I, H] -> its gate rows then its up rows of this rank, w2 [E, H, I] ->
+    its columns. Returns (w13_local, w2_local, intermediate_offset); the scales are NOT sliced (the kernels index the
+    unsharded scale tensors by global position). Works on any device."""
+    E, two_i, _ = w13_q.shape
+    inter = two_i // 2
+    if inter % tp_size:
+        raise ValueError(f"intermediate size {inter} is not divisible by the tensor-parallel size {tp_size}")
+    ip = inter // tp_size
+    lo, hi = tp_rank * ip, (tp_rank + 1) * ip
+    b13, b2 = w13_q.view(torch.uint8), w2_q.view(torch.uint8)
+    w13_local = torch.cat([b13[:, lo:hi], b13[:, inter + lo:inter + hi]], dim=1).contiguous().view(w13_q.dtype)
+    w2_local = b2[:, :, lo:hi].contiguous().view(w2_q.dtype)
+    return w13_local, w2_local, lo
+
+
 def fused_experts_fp8_shard(hidden_states: torch.Tensor, w13_q: torch.Tensor, w13_scale: torch.Tensor,
                             w2_q: torch.Tensor, w2_scale: torch.Tensor, topk_weights: torch.Tensor,
                             topk_ids: torch.Tensor, intermediate_offset: int, intermediate_size: int,

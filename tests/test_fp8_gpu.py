@@ -170,10 +170,8 @@ def test_fp8_tensor_parallel_shards_use_the_unsharded_scale_blocks(T, H, E, k, I
     ip = I // tp
     parts = {}
     for r in ranks:
-        lo, hi = r * ip, (r + 1) * ip
-        b13, b2 = q13.view(torch.uint8), q2.view(torch.uint8)
-        q13r = torch.cat([b13[:, lo:hi], b13[:, I + lo:I + hi]], dim=1).contiguous().view(torch.float8_e4m3fn)
-        q2r = b2[:, :, lo:hi].contiguous().view(torch.float8_e4m3fn)
+        q13r, q2r, lo = fused_moe.shard_fp8_expert_weights(q13, q2, r, tp)
+        assert lo == r * ip
         want = O.fused_experts_fp8(x, q13r, s13, q2r, s2, tw, ti, i_offset=lo, i_total=I)
         got = fused_moe.fused_experts_fp8_shard(x.to(d), q13r.to(d), s13.to(d), q2r.to(d), s2.to(d), tw.to(d), ti.to(d),
                                                 lo, I).cpu()

@@ -62,6 +62,24 @@ def _worker(rank, world, port, q):
         full = O.fused_experts(x, w13, w2, tw, ti, mode="exact", w13_bias=b13, w2_bias=b2).float()
         assert O.rel_l2(part, full) < 8e-3
 
+        # fp8 shards: sliced like the bf16 weights, scales of the unsharded tensors; I / world = 192 puts rank 1's
+        # slice in the middle of a 128-wide scale block. The ranks' partial sums add up to the unsharded emulation
+        # (up to the finer quantisation groups of a split block).
+        from layered_prefill_b200 import fused_moe as fm
+        g8 = torch.Generator().manual_seed(3)
+        I8, H8 = 192 * world, 128
+        x8 = torch.randn(T, H8, generator=g8).to(torch.bfloat16)
+        q13, s13 = O.quant_weight_block_fp8((torch.randn(E, 2 * I8, H8, generator=g8) * 0.05).to(torch.bfloat16))
+        q2, s2 = O.quant_weight_block_fp8((torch.randn(E, H8, I8, generator=g8) * 0.05).to(torch.bfloat16))
+        q13r, q2r, off = fm.shard_fp8_expert_weights(q13, q2, rank, world)
+        assert off == rank * 192 and q13r.shape == (E, 384, H8) and q2r.shape == (E, H8, 192)
+        ref13, ref2 = O.shard_expert_weights(q13.view(torch.uint8), q2.view(torch.uint8), world, rank)
+        assert torch.equal(q13r.view(torch.uint8), ref13) and torch.equal(q2r.view(torch.uint8), ref2)
+        part8 = O.fused_experts_fp8(x8, q13r, s13, q2r, s2, tw, ti, i_offset=off, i_total=I8).float()
+        dist.all_reduce(part8)
+        full8 = O.fused_experts_fp8(x8, q13, s13, q2, s2, tw, ti).float()
+        assert O.rel_l2(part8, full8) < 3e-2
+
         # mapping of checkpoint names to (param, shard) as the loader uses it
         m = FusedMoE.make_expert_params_mapping("gate_proj", "down_proj", "up_proj", num_experts=E)
         assert len(m) == 3 * E and m[0] == ("experts.w13_", "experts.0.gate_proj.", 0, "w1")
