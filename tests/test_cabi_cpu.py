@@ -75,3 +75,37 @@ def test_host_mirror_rejects_cpu_tensors():
         fused_moe.fused_experts(x, w13, w2, None, None, torch.zeros(4, 1), torch.zeros(4, 1, dtype=torch.int32))
     with pytest.raises(ValueError):
         fused_moe.fused_experts(x.float(), w13, w2, None, None, torch.zeros(4, 1), torch.zeros(4, 1, dtype=torch.int32))
+
+
+def test_argument_errors_of_the_later_entry_points():
+    """fp8 experts, the norm ops and the call in front of the block: shape and pointer checks answer before any CUDA
+    call, so they can be exercised without a GPU."""
+    from layered_prefill_b200 import _lib
+    lib = _lib.lib
+    buf = ctypes.create_string_buffer(64)
+    p = ctypes.addressof(buf)
+    fp = ctypes.cast(p, ctypes.POINTER(ctypes.c_float))
+    big = 1 << 34
+    # fp8: H not a multiple of 128; slice of I not on a multiple of 64; slice past the end; missing workspace
+    assert lib.moe_b200_fused_experts_fp8(p, p, fp, p, fp, p, p, p, 4, 8, 2, 192, 128, p, big, p, None) == 1
+    assert "multiple of 128" in _lib.last_error()
+    assert lib.moe_b200_fused_experts_fp8_tp(p, p, fp, p, fp, p, p, p, 4, 8, 2, 128, 192, 32, 384, p, big, p, None) == 1
+    assert lib.moe_b200_fused_experts_fp8_tp(p, p, fp, p, fp, p, p, p, 4, 8, 2, 128, 192, 256, 384, p, big, p, None) == 1
+    assert lib.moe_b200_fused_experts_fp8_tp(p, p, fp, p, fp, p, p, p, 4, 8, 2, 128, 192, 192, 384, p, 16, p, None) == 3
+    assert "workspace" in _lib.last_error()
+    assert lib.moe_b200_fused_experts_fp8_tp(p, None, fp, p, fp, p, p, p, 4, 8, 2, 128, 192, 192, 384, p, big, p, None) == 1
+    assert lib.moe_b200_fused_experts_fp8_workspace_bytes(64, 128, 8, 2048, 768) > \
+        lib.moe_b200_fused_experts_workspace_bytes(64, 128, 8, 2048, 768)
+    assert lib.moe_b200_quant_fp8_per_token_group(p, 4, 100, p, fp, None) == 1   # row length not a multiple of 128
+    # norm ops: hidden size not a multiple of 8 / above the kernel's limit; null pointers
+    assert lib.moe_b200_rms_norm(p, p, p, 1e-6, 4, 100, None) == 1
+    assert lib.moe_b200_add_rms_norm(p, p, p, p, 1e-6, 4, 32000, None) == 1
+    assert lib.moe_b200_add_rms_norm(p, None, p, p, 1e-6, 4, 128, None) == 1
+    # the call in front of the block: k > E, H not a multiple of 16, the unfused path without its workspace
+    assert lib.moe_b200_add_rms_norm_router(p, p, p, 1e-6, p, p, None, fp, p, 4, 128, 8, 9, 1, p, big, p, None) == 1
+    assert lib.moe_b200_add_rms_norm_router(p, p, p, 1e-6, p, p, None, fp, p, 4, 120, 8, 2, 1, p, big, p, None) == 1
+    assert lib.moe_b200_add_rms_norm_router(p, p, p, 1e-6, p, p, None, fp, p, 4, 128, 16, 2, 1, None, 0, p, None) == 3
+    assert lib.moe_b200_pre_moe_workspace_bytes(4096, 2048, 128) >= 4096 * 128 * 2
+    # all-reduce additions: a null communicator is an argument error
+    assert lib.moe_b200_ar_register_fused_buffer(0, None, 64) == 1
+    assert lib.moe_b200_ar_all_reduce_add_rms_norm(0, p, p, p, p, 1e-6, p, 4, 128, p, 4096, 0, p, None) == 1
