@@ -12,14 +12,17 @@
 // Synchronisation: one monotonically increasing counter per (block, peer) slot; a waiter accepts any
 // value at or past the one it expects (signed difference), so a peer that is one barrier ahead cannot
 // be missed and a single slot array serves every barrier of a launch. Data written before a barrier
-// by thread i of block b is read after it only by thread i of block b on the peers, which is what the
-// block-level release/acquire guarantees. Every spin is bounded by a wall-clock limit; when it runs
+// by block b is read after it only by block b of the peers (every kernel below maps elements, or whole token
+// rows, to blocks the same way on both sides of a barrier), which is what the block-level
+// release/acquire (__syncthreads + st.release / ld.acquire + __syncthreads) guarantees. Every spin is bounded by a wall-clock limit; when it runs
 // out the kernel stores a status word and finishes without waiting further.
 //
 // Peer data is read with ordinary 16-byte loads (ld.global.cg) from IPC-mapped buffers: no TMA, no
 // cluster features, nothing that depends on which GPU owns the memory.
-#include <map>
 #include <array>
+#include <cstdlib>
+#include <cstring>
+#include <map>
 #include <string>
 #include <unordered_map>
 #include <vector>
@@ -261,10 +264,13 @@ __global__ void __launch_bounds__(kArThreads, 1) ar_oneshot_add_rms_norm_kernel(
 #pragma unroll
   for (int r = 0; r < N; ++r) ptrs[r] = static_cast<const uint4*>(rd.ptrs[r]);
   if (p.c3 != nullptr) {
-    const long long tid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
-    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    // Phase 0 is row-owned like the reduction below: block b of a peer reads, after the barrier, exactly the
+    // rows that block b of this rank wrote before it (the barrier pairs same-numbered blocks only).
     uint4* own = const_cast<uint4*>(ptrs[p.rank]);
-    for (long long v = tid; v < p.nvec; v += stride) slot_sum_vec(p, own, v);
+    for (int row = blockIdx.x; row < nt.T; row += gridDim.x) {
+      const long long row_vec = static_cast<long long>(row) * p.hidden_vecs;
+      for (int c = threadIdx.x; c < p.hidden_vecs; c += blockDim.x) slot_sum_vec(p, own, row_vec + c);
+    }
   }
   peer_barrier<N>(p, true, &timed_out);
   for (int row = blockIdx.x; row < nt.T; row += gridDim.x) {
@@ -350,6 +356,7 @@ struct Comm {
   std::vector<void*> graph_unreg;
   std::map<IpcKey, char*> ipc_opened;
   unsigned long long wait_limit_ns = kWaitLimitNs;
+  int env_algo = 0;               // 1 = one-shot, 2 = two-shot forced by VLLM_CUSTOM_ALLREDUCE_ALGO at init time
   RankData* fused_rd = nullptr;   // the double buffer of the barrier-saving one-shot kernel (registered, used by nothing else)
   long long fused_bytes = 0;
 };
@@ -379,6 +386,7 @@ int pick_blocks(long long nvec) {
 }
 
 bool use_oneshot(const Comm& c, long long bytes, int algo) {
+  if (algo == 0) algo = c.env_algo;  // a call's own choice wins over the environment's
   if (algo == 1) return true;
   if (algo == 2) return false;
   if (c.world == 2) return true;
@@ -564,7 +572,15 @@ int moe_b200_ar_init(const int64_t* meta_ptrs, int world_size, void* rank_data, 
   if (world_size > kMaxRanks) return set_error(kStatusInvalidArgument, "world size > 8 is not supported");
   if (world_size % 2 == 1) return set_error(kStatusInvalidArgument, "Odd num gpus is not supported for now");
   if (rank < 0 || rank >= world_size) return set_error(kStatusInvalidArgument, "invalid rank passed in");
+  // The reference's environment override of the algorithm choice (csrc/custom_all_reduce.cuh:561-577), read once.
+  int env_algo = 0;
+  if (const char* env = getenv("VLLM_CUSTOM_ALLREDUCE_ALGO")) {
+    if (strcmp(env, "1stage") == 0 || strcmp(env, "oneshot") == 0) env_algo = 1;
+    else if (strcmp(env, "2stage") == 0 || strcmp(env, "twoshot") == 0) env_algo = 2;
+    else return set_error(kStatusInvalidArgument, "Invalid VLLM_CUSTOM_ALLREDUCE_ALGO: %s. Valid values: 1stage, oneshot, 2stage, twoshot", env);
+  }
   Comm* c = new Comm();
+  c->env_algo = env_algo;
   c->rank = rank;
   c->world = world_size;
   c->fully_connected = fully_connected != 0;

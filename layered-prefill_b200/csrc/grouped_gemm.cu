@@ -11,15 +11,18 @@
 //     into a shared-memory ring that takes all 227 KB (4 stages at N=256, 5 at N=192, 7 at N=128); the
 //     token rows (hidden states gathered through the permutation in pass 1, rows of the permuted
 //     intermediate in pass 2) come in with 16-byte cp.async from four warps, written straight into the
-//     same swizzled K-major layout, and signal the stage's barrier asynchronously
-//     (cp.async.mbarrier.arrive.noinc). Splitting the operands over the TMA unit and the LSU path
-//     measured faster than TMA for both, and padding rows cost no traffic (zero-fill);
+//     same swizzled K-major layout; a stage is handed to the tensor core one stage late, after its copies
+//     completed and a fence.proxy.async (generic-proxy writes before async-proxy reads, CpAsyncStageHandOff
+//     in ptx.cuh). Splitting the operands over the TMA unit and the LSU path measured faster than TMA for
+//     both, and padding rows cost no traffic (zero-fill);
 //   * one thread issues tcgen05.mma (M=128, N<=256, K=16 per instruction) into one of two 256-column
 //     TMEM accumulators, so the epilogue of tile i overlaps the main loop of tile i+1;
 //   * pass 1 keeps the gate rows and the matching up rows of w13 in the same tile (columns [0,BNH)
 //     and [BNH,2BNH) of the accumulator), so the activation is applied in registers with the
 //     reference's three bf16 roundings and only h is written, in permuted order;
-//   * pass 2 scales by the routed weight and writes bf16 rows at their flat index t*k+j.
+//   * pass 2 scales by the routed weight and writes bf16 rows at their flat index t*k+j; an epilogue warp owns
+//     one row per lane (the TMEM layout), so it turns 64 columns of its 32 rows around in a 4 KB shared-memory
+//     patch and stores whole 128-byte lines (four rows per instruction) instead of 32 scattered 16-byte pieces.
 // The tile list is static: tile = blockIdx.x + i*gridDim.x over (m_block, n_tile), n fastest.
 #include <cmath>
 #include <cstdio>
@@ -42,6 +45,7 @@ constexpr int kAccCols = 256;
 constexpr int kTmemCols = 512;
 constexpr int kBarrierBytes = 1024;                      // barriers + TMEM slot, in front of the ring
 constexpr int kSmemLimit = 227 * 1024;                   // opt-in shared memory per CTA on sm_100
+constexpr int kPatchBytes = 32 * 128;                    // per epilogue warp (down pass): 32 rows x 64 bf16 columns
 constexpr int kRingBudget = kSmemLimit - kBarrierBytes - 1024 /*alignment slack*/;
 
 constexpr int kWarpTma = 0;
@@ -82,10 +86,11 @@ union Pack8 {
 __device__ __forceinline__ void report(int* status, int code) { atomicCAS(status, 0, code); }
 
 // Epilogue of one 128-row tile for the 32 rows one warp may read from TMEM (taddr = its lane quarter and
-// the accumulator's first column). pos = permuted row, flat = t*k+j of that row (>= numel on padding rows).
+// the accumulator's first column). pos = permuted row, flat = t*k+j of that row (>= numel on padding rows);
+// patch = shared-memory address of this warp's 4 KB transposition patch (down pass only).
 template <int kMode>
 __device__ __forceinline__ void epilogue_rows(const KernelParams& p, uint32_t taddr, long long pos, int flat,
-                                              bool valid, float w, int e, int n0) {
+                                              bool valid, float w, int e, int n0, uint32_t patch) {
   if (kMode == 1) {
     __nv_bfloat16* out_row = p.out + pos * p.out_ld;
     if (!p.interleaved) {
@@ -150,24 +155,41 @@ __device__ __forceinline__ void epilogue_rows(const KernelParams& p, uint32_t ta
       }
     }
   } else {
-    __nv_bfloat16* out_row = p.out + static_cast<long long>(valid ? flat : 0) * p.out_ld;
     const __nv_bfloat16* bias_d = p.bias ? p.bias + static_cast<long long>(e) * p.out_cols : nullptr;
-    for (int c = 0; c < p.tile_cols; c += 16) {
-      uint32_t d[16];
-      tmem_ld_x16(taddr + c, d);
+    const int lane = threadIdx.x & 31;
+    const uint32_t patch_w = patch + static_cast<uint32_t>(lane) * 128u;  // this lane's row of the patch
+    const int chunk = lane & 7;   // read side: 16-byte piece of a row
+    const int rsub = lane >> 3;   // read side: row inside a group of four
+    for (int c0 = 0; c0 < p.tile_cols; c0 += 64) {
+      uint32_t d[4][16];
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4) tmem_ld_x16(taddr + c0 + 16 * q4, d[q4]);
       tmem_ld_wait();
-      const int col = n0 + c;
-      if (valid && col < p.out_cols) {
+      const int col0 = n0 + c0;
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4) {
         Pack8 o[2];
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
-          float v = __uint_as_float(d[j]);
-          if (bias_d) v += __bfloat162float(bias_d[col + j]);
+          float v = __uint_as_float(d[q4][j]);
+          if (bias_d && col0 + 16 * q4 + j < p.out_cols) v += __bfloat162float(bias_d[col0 + 16 * q4 + j]);
           o[j >> 3].h[j & 7] = __float2bfloat16_rn(v * w);
         }
-        *reinterpret_cast<uint4*>(out_row + col) = o[0].u;
-        *reinterpret_cast<uint4*>(out_row + col + 8) = o[1].u;
+        // row `lane`, pieces 2*q4 and 2*q4+1, xor-swizzled so that a quarter warp covers all 32 banks
+        st_shared_v4(patch_w + (static_cast<uint32_t>((2 * q4) ^ (lane & 7)) << 4), o[0].u);
+        st_shared_v4(patch_w + (static_cast<uint32_t>((2 * q4 + 1) ^ (lane & 7)) << 4), o[1].u);
       }
+      __syncwarp();
+      const int col = col0 + chunk * 8;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int r = rsub + 4 * i;
+        const int flat_r = __shfl_sync(0xffffffffu, flat, r);
+        const uint4 v = ld_shared_v4(patch + static_cast<uint32_t>(r) * 128u + (static_cast<uint32_t>(chunk ^ (r & 7)) << 4));
+        if (flat_r < p.numel && col < p.out_cols)
+          *reinterpret_cast<uint4*>(p.out + static_cast<long long>(flat_r) * p.out_ld + col) = v;
+      }
+      __syncwarp();  // the patch is rewritten by the next 64 columns
     }
   }
 }
@@ -313,6 +335,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b, const KernelPara
     // ------------------------------------------------------------------ epilogue
     const int q = warp & 3;  // TMEM lane quarter this warp may read
     const int row_in_tile = q * 32 + lane;
+    const uint32_t patch = smem_u32(ring) + num_stages * stage_bytes + static_cast<uint32_t>(q) * kPatchBytes;
     uint32_t tile_iter = 0;
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++tile_iter) {
       const uint32_t acc = tile_iter & 1u;
@@ -336,7 +359,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b, const KernelPara
 
       if (__any_sync(0xffffffffu, valid)) {
         const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * kAccCols;
-        epilogue_rows<kMode>(p, taddr, pos, flat, valid, w, e, n0);
+        epilogue_rows<kMode>(p, taddr, pos, flat, valid, w, e, n0, patch);
       }
       tc_fence_before_sync();
       __syncwarp();
@@ -349,6 +372,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b, const KernelPara
     const int ch = lane & 7;             // 16-byte chunk inside the 128-byte row
     const int row0 = gw * 4 + sub;       // rows handled: row0 + 16*i
     const uint32_t swz = static_cast<uint32_t>((ch ^ (row0 & 7)) << 4);
+    CpAsyncStageHandOff hand_off;
     uint32_t s = 0, ph = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
@@ -363,11 +387,14 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b, const KernelPara
           src[i] = flat < p.numel ? p.x + (static_cast<long long>(m_blk) * BM + row0 + 16 * i) * p.K + ch * 8 : nullptr;
       }
       for (int kb = 0; kb < num_kb; ++kb) {
-        ok = mbar_wait(&bar_empty[s], ph ^ 1u);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) {
-          if (lane == 0) report(p.status, kErrWaitEmpty);
-          break;
+        if (!__all_sync(0xffffffffu, mbar_try_wait(&bar_empty[s], ph ^ 1u))) {
+          hand_off.flush();  // the ring is full: nothing to overlap with, publish the outstanding stage first
+          ok = mbar_wait(&bar_empty[s], ph ^ 1u);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) {
+            if (lane == 0) report(p.status, kErrWaitEmpty);
+            break;
+          }
         }
         const uint32_t a_base = smem_u32(ring + s * stage_bytes);
         const bool in_k = kb * BK + ch * 8 < p.K;
@@ -378,15 +405,14 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b, const KernelPara
           cp_async_16(dst, live ? static_cast<const void*>(src[i] + kb * BK) : static_cast<const void*>(p.x),
                       live ? 16u : 0u);
         }
-        // the stage's barrier counts this thread as arrived once the copies above have landed
-        cp_async_mbar_arrive_noinc(&bar_full[s]);
+        hand_off.issued(&bar_full[s]);
         if (++s == num_stages) {
           s = 0;
           ph ^= 1u;
         }
       }
     }
-    cp_async_wait_all();
+    hand_off.flush();
   }
 
   tc_fence_before_sync();
@@ -398,11 +424,14 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b, const KernelPara
 // ---------------------------------------------------------------- host side
 template <int kMode>
 int ensure_smem_attr() {
-  static bool done = false;
-  if (!done) {
+  // the attribute belongs to the function on one device: a process that drives several GPUs sets it on each
+  static bool done[64] = {false};
+  int dev = 0;
+  if (int st = check_cuda(cudaGetDevice(&dev), "cudaGetDevice")) return st;
+  if (dev < 0 || dev >= 64 || !done[dev]) {
     const cudaError_t e = cudaFuncSetAttribute(grouped_gemm_kernel<kMode>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit);
     if (e != cudaSuccess) return check_cuda(e, "cudaFuncSetAttribute(grouped_gemm_kernel)");
-    done = true;
+    if (dev >= 0 && dev < 64) done[dev] = true;
   }
   return kStatusOk;
 }
@@ -431,9 +460,9 @@ int pick_down_tile(int hidden, double m_blocks) {
 }
 
 // Ring depth that fits the shared-memory budget for a given accumulator width.
-void pick_ring(int mma_n, int* stages, int* stage_bytes) {
+void pick_ring(int mma_n, int reserve_bytes, int* stages, int* stage_bytes) {
   *stage_bytes = kABytes + mma_n * 128;
-  int s = kRingBudget / *stage_bytes;
+  int s = (kRingBudget - reserve_bytes) / *stage_bytes;
   if (s > kMaxStages) s = kMaxStages;
   *stages = s;
 }
@@ -535,7 +564,7 @@ int launch_grouped_gemm1(const GroupedGemmArgs& a, const __nv_bfloat16* x, const
   p.interleaved = a.activation == 1 ? 1 : 0;
   p.out = h_sorted; p.out_ld = a.inter; p.topk_w = nullptr; p.bias = w13_bias;
   p.alpha = a.act_alpha; p.limit = a.act_limit; p.status = a.status;
-  pick_ring(mma_n, &p.stages, &p.stage_bytes);
+  pick_ring(mma_n, 0, &p.stages, &p.stage_bytes);
   (void)rows_cap;
 
   long long tiles = static_cast<long long>(a.max_m_blocks) * p.n_tiles;
@@ -570,11 +599,11 @@ int launch_grouped_gemm2(const GroupedGemmArgs& a, const __nv_bfloat16* h_sorted
   p.out_cols = a.hidden; p.inter = a.inter; p.interleaved = 0;
   p.out = c3; p.out_ld = a.hidden; p.topk_w = topk_w; p.bias = w2_bias;
   p.alpha = 0.f; p.limit = 0.f; p.status = a.status;
-  pick_ring(p.mma_n, &p.stages, &p.stage_bytes);
+  pick_ring(p.mma_n, 4 * kPatchBytes, &p.stages, &p.stage_bytes);
 
   long long tiles = static_cast<long long>(a.max_m_blocks) * p.n_tiles;
   const int grid = static_cast<int>(tiles < device_sm_count() ? tiles : device_sm_count());
-  const int smem_bytes = kBarrierBytes + 1024 + p.stages * p.stage_bytes;
+  const int smem_bytes = kBarrierBytes + 1024 + p.stages * p.stage_bytes + 4 * kPatchBytes;
   if (int st = check_cuda(launch_pdl(grouped_gemm_kernel<2>, dim3(grid), dim3(kThreads), smem_bytes, stream, map_b, p),
                           "grouped_gemm down launch"))
     return st;

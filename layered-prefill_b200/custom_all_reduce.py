@@ -185,13 +185,24 @@ class CustomAllreduce:
         return self.all_reduce(input, registered=False)
 
     def close(self) -> None:
+        """Collective over the CPU group: every rank closes its mappings of the peers' buffers, all ranks meet,
+        and only then each frees its own allocations (a cudaFree of memory a peer still maps is deferred by the
+        driver, and an unclosed mapping leaks)."""
         if not self.disabled and self._ptr:
             ops.dispose(self._ptr)
             self._ptr = 0
+            self.disabled = True
+            for ptrs in (self.meta_ptrs, self.buffer_ptrs, self.fused_ptrs):
+                for i, p in enumerate(ptrs):
+                    if i != self.rank and p:
+                        ops.close_mem_handle(p)
+            try:
+                dist.barrier(group=self.gloo_group)
+            except Exception:  # noqa: BLE001  (group already destroyed, or a peer is gone: free anyway)
+                pass
             self.free_shared_buffer(self.meta_ptrs, rank=self.rank)
             self.free_shared_buffer(self.buffer_ptrs, rank=self.rank)
             self.free_shared_buffer(self.fused_ptrs, rank=self.rank)
-            self.disabled = True
 
     def __del__(self):
         try:

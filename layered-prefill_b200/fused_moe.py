@@ -55,21 +55,43 @@ def moe_align_block_size(topk_ids: torch.Tensor, block_size: int, num_experts: i
 
 
 class _Workspaces:
-    """One growing scratch tensor per device, reused across calls (stable address, no per-call malloc)."""
+    """One scratch tensor per device, reused across calls (no per-call malloc). It grows when a larger request
+    comes; outgrown tensors are kept alive, because a CUDA graph captured earlier still holds their address.
+    Growing inside a stream capture is refused (the new tensor would belong to the capture's private pool):
+    call `reserve_workspace` for the largest batch before capturing. All streams of a device share the buffer,
+    so calls on different streams must be ordered by the caller."""
 
     def __init__(self) -> None:
         self._buf: dict[int, torch.Tensor] = {}
+        self._outgrown: list[torch.Tensor] = []
 
     def get(self, device: torch.device, nbytes: int) -> torch.Tensor:
         idx = device.index if device.index is not None else torch.cuda.current_device()
         cur = self._buf.get(idx)
         if cur is None or cur.numel() < nbytes:
+            if torch.cuda.is_current_stream_capturing():
+                raise RuntimeError(
+                    f"the MoE workspace would have to grow to {nbytes} bytes inside a CUDA-graph capture; "
+                    "call fused_moe.reserve_workspace(...) for the largest batch before capturing")
+            if cur is not None:
+                self._outgrown.append(cur)
             cur = torch.empty(max(nbytes, 1), dtype=torch.uint8, device=torch.device("cuda", idx))
             self._buf[idx] = cur
         return cur
 
 
 _workspaces = _Workspaces()
+
+
+def reserve_workspace(device: torch.device, max_tokens: int, num_experts: int, top_k: int, hidden_size: int,
+                      intermediate_size_per_partition: int, fp8: bool = False) -> int:
+    """Sizes the device's scratch buffer for batches of up to `max_tokens` tokens, so that later calls (inside
+    CUDA-graph captures too) never allocate. Returns the size in bytes."""
+    args = (int(max_tokens), int(num_experts), int(top_k), int(hidden_size), int(intermediate_size_per_partition))
+    nbytes = max(lib.moe_b200_fused_moe_workspace_bytes(*args),
+                 lib.moe_b200_fused_experts_fp8_workspace_bytes(*args) if fp8 else 0)
+    _workspaces.get(device, nbytes)
+    return int(nbytes)
 
 
 def _check_experts_args(hidden_states, w1, w2, topk_weights, topk_ids, activation, **quant):

@@ -35,6 +35,11 @@ def status_word(device: torch.device) -> torch.Tensor:
     return _status_words[idx]
 
 
+def launch_count() -> int:
+    """Kernels this library has launched in this process so far (graph replays are not seen)."""
+    return int(lib.moe_b200_launch_count())
+
+
 def read_status(device: torch.device | None = None) -> int:
     """Synchronise the current stream and return the device status word (0 = no device-side timeout)."""
     dev = device if device is not None else torch.device("cuda", torch.cuda.current_device())
@@ -173,6 +178,11 @@ def open_mem_handle(handle: bytes) -> int:
     ptr = ctypes.c_int64(0)
     check(lib.moe_b200_ar_open_mem_handle(buf, ctypes.byref(ptr)))
     return int(ptr.value)
+
+
+def close_mem_handle(ptr: int) -> None:
+    """Unmaps a peer's buffer opened with open_mem_handle (the reference leaves this to process exit)."""
+    check(lib.moe_b200_ar_close_mem_handle(int(ptr)))
 
 
 def free_shared_buffer(ptr: int) -> None:

@@ -68,4 +68,7 @@ def main(ref_root: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("REFERENCE_ROOT")
+    if not root:
+        raise SystemExit("usage: make_golden.py <path of the reference tree>   (or REFERENCE_ROOT=<path>)")
+    main(root)

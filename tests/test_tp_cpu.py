@@ -112,6 +112,30 @@ def _worker(rank, world, port, q):
         finally:
             car.ops = real
         assert ptrs == [1000 + r if r == rank else 2000 + r for r in range(world)]
+        # close(): every mapping of a peer's buffer is closed, the ranks meet, then each frees its own three buffers
+        calls = []
+
+        class FakeLifecycleOps:
+            dispose = staticmethod(lambda p: calls.append(("dispose", p)))
+            close_mem_handle = staticmethod(lambda p: calls.append(("close", p)))
+            free_shared_buffer = staticmethod(lambda p: calls.append(("free", p)))
+        c2 = car.CustomAllreduce.__new__(car.CustomAllreduce)
+        c2.disabled, c2._ptr, c2.rank, c2.gloo_group = False, 77, rank, comm.gloo_group
+        c2.meta_ptrs = [10 + r for r in range(world)]
+        c2.buffer_ptrs = [20 + r for r in range(world)]
+        c2.fused_ptrs = [30 + r for r in range(world)]
+        car.ops = FakeLifecycleOps
+        try:
+            c2.close()
+            c2.close()  # idempotent
+        finally:
+            car.ops = real
+        assert calls[0] == ("dispose", 77) and c2.disabled and c2._ptr == 0
+        closes = [c for c in calls if c[0] == "close"]
+        frees = [c for c in calls if c[0] == "free"]
+        assert sorted(p for _, p in closes) == sorted(b + r for b in (10, 20, 30) for r in range(world) if r != rank)
+        assert [p for _, p in frees] == [10 + rank, 20 + rank, 30 + rank]
+        assert max(calls.index(c) for c in closes) < min(calls.index(f) for f in frees)
         assert not car.is_weak_contiguous(torch.zeros(4, 4)[:, :2]) and car.is_weak_contiguous(torch.zeros(4, 4)[2:])
         dist.barrier()
         dist.destroy_process_group()

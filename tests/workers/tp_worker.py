@@ -103,6 +103,31 @@ def main():
     red = layer.maybe_all_reduce_tensor_model_parallel(part)
     assert torch.equal(red, out)
 
+    # ---- 3b. benchmark shapes at full size: the decode configuration (T=64, H=2048, E=128, top-8, I=768; at 8 ranks
+    # I/tp = 96, one 96-column gate_up tile per expert) and the 235B layer's widths (H=4096, I=1536: I/tp = 192 at 8
+    # ranks; 32 of its 128 experts, to bound host memory) through the one-call block with the fused reduction
+    from layered_prefill_b200 import workload as W
+    cases = [W.WORKLOADS["qwen3-30b-a3b-decode-t64"]]
+    if world == 8:
+        cases.append(W.MoeWorkload("qwen3-235b-a22b-widths-e32-t64", 64, 4096, 32, 8, 1536))
+    for wl in cases:
+        inp = W.make_inputs(wl, seed=0)
+        want = O.moe_block_tp(inp["x"], inp["router_logits"], inp["w13"], inp["w2"], wl.top_k, world)
+        sh13, sh2 = O.shard_expert_weights(inp["w13"], inp["w2"], world, rank)
+        xd, lgd, w13d, w2d = inp["x"].to(dev), inp["router_logits"].to(dev), sh13.to(dev), sh2.to(dev)
+        outs = []
+        for rep in range(3):  # repeated calls alternate the halves of the fused buffer
+            outs.append(fused_moe.fused_moe_forward(xd, lgd, w13d, w2d, wl.top_k, True, inplace=False, comm=comm))
+        torch.cuda.synchronize()
+        assert ops.read_status(dev) == 0
+        rl, ma = O.rel_l2(outs[0].cpu(), want), O.max_abs(outs[0].cpu(), want)
+        assert rl <= 5e-3 and ma <= 2e-2, (wl.name, rl, ma)
+        assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+        gathered = [torch.empty_like(outs[0]) for _ in range(world)]
+        dist.all_gather(gathered, outs[0])
+        assert all(torch.equal(gathered[0], t) for t in gathered), wl.name
+        del inp, sh13, sh2, w13d, w2d
+
     # ---- 4. CUDA-graph capture of the all-reduce on an unregistered tensor: the address met during capture
     # is registered with the peers when the capture() context ends (custom_all_reduce.py:206-239)
     inp = torch.full((128, 1024), float(rank + 1), dtype=torch.bfloat16, device=dev)
@@ -150,6 +175,51 @@ def main():
         assert torch.equal(norm_a, norm_b), f"normed T={T}"
         assert torch.equal(red.cpu(), O.all_reduce(parts))
     assert ops.read_status(dev) == 0
+    # the same tail behind the k-slot sum (decode shapes), ranks deliberately out of step and calls back to back
+    # without host synchronisation: a block of a lagging peer must never be read before it wrote its rows
+    T, k, H, reps = 64, 8, 2048, 40
+    c3s, res0s = [], []
+    for variant in range(2):
+        per_rank = []
+        for r in range(world):
+            g = torch.Generator().manual_seed(900 + 10 * variant + r)
+            per_rank.append(torch.randn(T, k, H, generator=g).to(torch.bfloat16))
+        c3s.append(per_rank)
+        res0s.append((torch.randn(T, H, generator=torch.Generator().manual_seed(950 + variant)) * 2).to(torch.bfloat16))
+    wn = (1 + 0.1 * torch.randn(H, generator=torch.Generator().manual_seed(960))).to(torch.bfloat16)
+    mine = [per_rank[rank].to(dev) for per_rank in c3s]
+    wnd = wn.to(dev)
+    wants = []  # the separate steps, each synchronised: k-slot sum, all-reduce, add + norm
+    for variant in range(2):
+        part = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
+        ops.moe_sum(mine[variant], part)
+        red = comm.all_reduce(part, registered=False)
+        torch.cuda.synchronize()
+        assert torch.equal(red.cpu(), O.all_reduce([O.moe_sum(c) for c in c3s[variant]]))
+        res_w, norm_w = res0s[variant].to(dev).clone(), torch.empty(T, H, dtype=torch.bfloat16, device=dev)
+        ops.add_rms_norm(norm_w, res_w, red, wnd, 1e-6)
+        torch.cuda.synchronize()
+        wants.append((norm_w.cpu(), res_w.cpu()))
+        dist.barrier()
+    res_bufs = torch.stack([res0s[i % 2] for i in range(reps)]).to(dev)
+    norm_bufs = torch.empty(reps, T, H, dtype=torch.bfloat16, device=dev)
+    scratch = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
+    stream = torch.cuda.current_stream().cuda_stream
+    dist.barrier()
+    for i in range(reps):
+        if (i + rank) % 5 == 0:
+            torch.cuda._sleep(300_000 * (1 + rank % 3))
+        check(lib.moe_b200_ar_moe_sum_all_reduce_add_rms_norm(
+            comm._ptr, mine[i % 2].data_ptr(), scratch.data_ptr(), res_bufs[i].data_ptr(), wnd.data_ptr(), 1e-6,
+            norm_bufs[i].data_ptr(), T, k, H, comm.buffer_ptrs[rank], comm.max_size, 0,
+            ops.status_word(dev).data_ptr(), stream))
+    torch.cuda.synchronize()
+    assert ops.read_status(dev) == 0
+    for i in range(reps):
+        want_norm, want_res = wants[i % 2]
+        assert torch.equal(res_bufs[i].cpu(), want_res), f"norm-tailed fused reduction, residual of call {i}"
+        assert torch.equal(norm_bufs[i].cpu(), want_norm), f"norm-tailed fused reduction, call {i}"
+
     # the block with that tail, through the FusedMoE mirror: same bits as block -> all-reduce -> add_rms_norm
     layer.reduce_results = True
     res0 = (torch.randn(T := 96, H := 512, generator=torch.Generator().manual_seed(77)) * 2).to(torch.bfloat16)
