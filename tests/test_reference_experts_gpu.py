@@ -51,9 +51,12 @@ def _dev():
     return torch.device("cuda", 0)
 
 
-def _bounds(got, want, what):
+def _bounds(got, want, what, scaled=False):
+    """max-abs <= 2e-2 and relative L2 <= 5e-3. scaled=True (the synthetic variants below, whose outputs reach
+    magnitudes of 4 to 30 where one bf16 ulp alone exceeds 2e-2) allows two bf16 ulps of the largest output."""
     ma, rl = O.max_abs(got, want), O.rel_l2(got, want)
-    assert rl <= REL_L2 and ma <= MAX_ABS, f"{what}: rel-L2 {rl:.3e}, max-abs {ma:.3e}"
+    bound = max(MAX_ABS, 2 ** -7 * float(want.float().abs().max())) if scaled else MAX_ABS
+    assert rl <= REL_L2 and ma <= bound, f"{what}: rel-L2 {rl:.3e}, max-abs {ma:.3e} (bound {bound:.3e})"
     return ma, rl
 
 
@@ -114,9 +117,9 @@ def test_variants_against_reference(ref, T, H, E, k, I, activation, bias):
     got = fused_moe.fused_experts(xd, w13d, w2d, b13d, b2d, otw, oti, inplace=False, activation=activation)
     torch.cuda.synchronize()
     assert ops.read_status(d) == 0
-    _bounds(got.cpu(), rout.cpu(), "ours vs reference")
+    _bounds(got.cpu(), rout.cpu(), "ours vs reference", scaled=True)
     want = O.fused_experts(x, w13, w2, rtw.cpu(), rti.cpu(), activation, "ref_rounding", b13, b2)
-    _bounds(want, rout.cpu(), "oracle vs reference")
+    _bounds(want, rout.cpu(), "oracle vs reference", scaled=True)
 
 
 def _fill_through_loaders(layers, E, I, H, bias, seed):
@@ -164,13 +167,13 @@ def test_fused_moe_layer_against_reference_layer(ref, single_rank_group, activat
     torch.cuda.synchronize()
     assert ops.read_status(d) == 0
     assert oout.data_ptr() == xo.data_ptr() and rout.data_ptr() == xr.data_ptr()  # both overwrite their input
-    _bounds(oout.cpu(), rout.cpu(), "FusedMoE.forward vs the reference's")
+    _bounds(oout.cpu(), rout.cpu(), "FusedMoE.forward vs the reference's", scaled=True)
     # and the CPU oracle on the loaded weights
     b13 = om.w13_bias.cpu() if bias else None
     b2 = om.w2_bias.cpu() if bias else None
     tw, ti, _ = O.fused_topk(x.cpu(), lg.cpu(), k, True)
     want = O.fused_experts(x.cpu(), om.w13_weight.cpu(), om.w2_weight.cpu(), tw, ti, activation, "ref_rounding", b13, b2)
-    _bounds(oout.cpu(), want, "FusedMoE.forward vs oracle")
+    _bounds(oout.cpu(), want, "FusedMoE.forward vs oracle", scaled=True)
 
 
 def test_library_patched_into_the_reference_sparse_moe_block(ref, single_rank_group, monkeypatch):
@@ -208,4 +211,4 @@ def test_library_patched_into_the_reference_sparse_moe_block(ref, single_rank_gr
             assert ops.launch_count() - launches0 >= 4, "the patched block did not run this library's kernels"
         torch.cuda.synchronize()
         assert ops.read_status(d) == 0
-        _bounds(got.cpu(), want.cpu(), f"patched sparse MoE block, T={T}")
+        _bounds(got.cpu(), want.cpu(), f"patched sparse MoE block, T={T}", scaled=True)
