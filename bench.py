@@ -597,14 +597,10 @@ def kernel_rooflines(ctx: Ctx, wl, rec, st):
         if rc != 0:
             raise SystemExit("gate_up launch failed: " + lib.moe_b200_last_error().decode())
 
-    comb = torch.empty(wl.T, wl.H, dtype=torch.bfloat16, device=dev)
-    counters = torch.zeros(lib.moe_b200_combine_counter_bytes(wl.T, wl.H) // 4, dtype=torch.int32, device=dev)
-
-    def down(i):  # the down pass as the block runs it: slot rows + top-k combine in its epilogue
-        rc = lib.moe_b200_grouped_gemm_down_combine(h_sorted.data_ptr(), rows_cap, sets[i % n_sets][1].data_ptr(), 0,
-                                                    tw.data_ptr(), s_pad.data_ptr(), e_ids.data_ptr(), post.data_ptr(),
-                                                    c3.data_ptr(), comb.data_ptr(), counters.data_ptr(), wl.T, wl.E,
-                                                    wl.top_k, wl.H, ip, stw, stream)
+    def down(i):
+        rc = lib.moe_b200_grouped_gemm_down(h_sorted.data_ptr(), rows_cap, sets[i % n_sets][1].data_ptr(), 0,
+                                            tw.data_ptr(), s_pad.data_ptr(), e_ids.data_ptr(), post.data_ptr(),
+                                            c3.data_ptr(), wl.T, wl.E, wl.top_k, wl.H, ip, stw, stream)
         if rc != 0:
             raise SystemExit("down launch failed: " + lib.moe_b200_last_error().decode())
 
@@ -625,7 +621,7 @@ def kernel_rooflines(ctx: Ctx, wl, rec, st):
                     "unit": "TFLOP/s", "frac": kernels["gate_up"]["frac_of_burst"], "traffic": traffic}
     else:
         by = {"gate_up": n_active * 2 * ip * wl.H * 2 + wl.T * wl.H * 2 + wl.T * wl.top_k * ip * 2,
-              "down": n_active * wl.H * ip * 2 + wl.T * wl.top_k * ip * 2 + wl.T * wl.top_k * wl.H * 2 + wl.T * wl.H * 2}
+              "down": n_active * wl.H * ip * 2 + wl.T * wl.top_k * ip * 2 + wl.T * wl.top_k * wl.H * 2}
         for name, ms in (("gate_up", gu_ms), ("down", dn_ms)):
             ach = by[name] / (ms * 1e-3) / 1e9
             kernels[name] = {"us_per_launch": ms * 1e3, "bytes_per_launch": by[name], "achieved_gbs": ach,

@@ -207,19 +207,6 @@ int moe_b200_grouped_gemm_down(const void* h_sorted, int rows_cap, const void* w
                                const float* topk_weights, const int32_t* sorted_token_ids, const int32_t* expert_ids,
                                const int32_t* num_tokens_post_pad, void* c3, int T, int E, int top_k, int H, int I,
                                int32_t* status_word, void* stream);
-/*
- * The down pass with the top-k combine in its epilogue: for_moe/fused_moe.py:611-631 (second
- * invoke_fused_moe_kernel call + moe_sum) as one launch. Besides the slot rows c3 it writes
- * out[t, :] = bf16(sum_j float(c3[t*k + j, :])), j ascending (moe_easy_kernel.py:26-31), each row by whichever
- * slot of the token finishes last. counters: moe_b200_combine_counter_bytes(T, H) bytes of device memory that
- * are ZERO when the call starts (the call leaves them zero again); out may not alias h_sorted or c3.
- */
-size_t moe_b200_combine_counter_bytes(int T, int H);
-int moe_b200_grouped_gemm_down_combine(const void* h_sorted, int rows_cap, const void* w2, const void* w2_bias,
-                                       const float* topk_weights, const int32_t* sorted_token_ids,
-                                       const int32_t* expert_ids, const int32_t* num_tokens_post_pad, void* c3,
-                                       void* out, int32_t* counters, int T, int E, int top_k, int H, int I,
-                                       int32_t* status_word, void* stream);
 
 /*
  * Router + fused_experts in one call: what FusedMoE.forward runs on one rank before the

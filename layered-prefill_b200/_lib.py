@@ -51,8 +51,6 @@ SIGNATURES = {
     "moe_b200_launch_count": (ctypes.c_uint64, []),
     "moe_b200_grouped_gemm_gate_up": (c_int, [c_void_p] * 7 + [c_int] * 7 + [c_void_p, c_void_p]),
     "moe_b200_grouped_gemm_down": (c_int, [c_void_p, c_int] + [c_void_p] * 7 + [c_int] * 5 + [c_void_p, c_void_p]),
-    "moe_b200_combine_counter_bytes": (c_size_t, [c_int, c_int]),
-    "moe_b200_grouped_gemm_down_combine": (c_int, [c_void_p, c_int] + [c_void_p] * 9 + [c_int] * 5 + [c_void_p, c_void_p]),
     "moe_b200_rms_norm": (c_int, [c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_void_p]),
     "moe_b200_add_rms_norm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_void_p]),
     "moe_b200_pre_moe_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),

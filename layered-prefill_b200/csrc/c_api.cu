@@ -67,8 +67,6 @@ struct ExpertsWorkspace {
   size_t align_ws_bytes;
   __nv_bfloat16* h_sorted;
   __nv_bfloat16* c3;
-  int* combine_cnt;        // arrival counters of the top-k combine inside the down pass
-  __nv_bfloat16* partial;  // [T, H] combined result of this rank when an all-reduce follows
   size_t total;
 };
 
@@ -84,8 +82,6 @@ ExpertsWorkspace carve_experts(void* base, int T, int E, int top_k, int H, int I
   w.align_ws = p + off; off += w.align_ws_bytes;
   w.h_sorted = reinterpret_cast<__nv_bfloat16*>(p + off); off += align_up(sizeof(__nv_bfloat16) * static_cast<size_t>(ps.sorted_cap) * I);
   w.c3 = reinterpret_cast<__nv_bfloat16*>(p + off); off += align_up(sizeof(__nv_bfloat16) * static_cast<size_t>(ps.numel) * H);
-  w.combine_cnt = reinterpret_cast<int*>(p + off); off += align_up(sizeof(int) * static_cast<size_t>(combine_counter_ints(T > 0 ? T : 1, H)));
-  w.partial = reinterpret_cast<__nv_bfloat16*>(p + off); off += align_up(sizeof(__nv_bfloat16) * static_cast<size_t>(T > 0 ? T : 1) * H);
   w.total = off;
   return w;
 }
@@ -128,12 +124,10 @@ int check_block_shapes(int T, int E, int top_k, int H, int I) {
 
 }  // namespace
 
-// The whole of fused_experts: permutation, gate_up pass, down pass with the top-k combine in its epilogue. The slot
-// rows C3 stay in the workspace; `combined` (bf16 [T, H], may be the caller's output, may alias x) receives
-// bf16(sum_j C3[t, j]).
-int run_experts(const void* x, const void* w13, const void* w2, const void* w13_bias, const void* w2_bias,
-                const float* topk_weights, const int* topk_ids, int T, int E, int top_k, int H, int I, int activation,
-                const ExpertsWorkspace& w, void* combined, int* status_word, cudaStream_t stream) {
+// Everything of fused_experts up to (not including) the k-slot sum; leaves C3 in the workspace.
+int run_experts_until_c3(const void* x, const void* w13, const void* w2, const void* w13_bias, const void* w2_bias,
+                         const float* topk_weights, const int* topk_ids, int T, int E, int top_k, int H, int I,
+                         int activation, const ExpertsWorkspace& w, int* status_word, cudaStream_t stream) {
   const PermSizes ps = perm_sizes(T, E, top_k);
   if (int st = launch_align_block_size(topk_ids, ps.numel, E, kBlockM, w.sorted_ids, ps.sorted_cap, w.expert_ids,
                                        ps.blocks_cap, w.num_post_pad, w.align_ws, w.align_ws_bytes, stream))
@@ -143,8 +137,6 @@ int run_experts(const void* x, const void* w13, const void* w2, const void* w13_
   a.numel = ps.numel; a.top_k = top_k; a.max_m_blocks = ps.blocks_cap; a.num_experts = E;
   a.hidden = H; a.inter = I; a.activation = activation; a.act_alpha = 1.702f; a.act_limit = 7.0f;
   a.status = status_word;
-  a.combine_counters = w.combine_cnt;
-  a.combine_out = static_cast<__nv_bfloat16*>(combined);
   if (int st = launch_grouped_gemm1(a, static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w13),
                                     static_cast<const __nv_bfloat16*>(w13_bias), w.h_sorted, ps.sorted_cap, stream))
     return st;
@@ -156,15 +148,15 @@ size_t experts_workspace_bytes(int T, int E, int top_k, int H, int I) {
   return carve_experts(nullptr, T, E, top_k, H, I).total;
 }
 
-// Runs the experts with the combined result in the workspace (this rank's partial sum, for the all-reduce).
-int run_experts_partial_ws(const void* x, const void* w13, const void* w2, const void* w13_bias, const void* w2_bias,
-                           const float* topk_weights, const int* topk_ids, int T, int E, int top_k, int H, int I,
-                           int activation, void* workspace, int* status_word, cudaStream_t stream,
-                           const __nv_bfloat16** partial_out) {
-  const ExpertsWorkspace w = carve_experts(workspace, T, E, top_k, H, I);
-  *partial_out = w.partial;
-  return run_experts(x, w13, w2, w13_bias, w2_bias, topk_weights, topk_ids, T, E, top_k, H, I, activation, w, w.partial,
-                     status_word, stream);
+const __nv_bfloat16* experts_workspace_c3(void* base, int T, int E, int top_k, int H, int I) {
+  return carve_experts(base, T, E, top_k, H, I).c3;
+}
+
+int run_experts_until_c3_ws(const void* x, const void* w13, const void* w2, const void* w13_bias, const void* w2_bias,
+                            const float* topk_weights, const int* topk_ids, int T, int E, int top_k, int H, int I,
+                            int activation, void* workspace, int* status_word, cudaStream_t stream) {
+  return run_experts_until_c3(x, w13, w2, w13_bias, w2_bias, topk_weights, topk_ids, T, E, top_k, H, I, activation,
+                              carve_experts(workspace, T, E, top_k, H, I), status_word, stream);
 }
 
 // all_reduce.cu
@@ -217,32 +209,6 @@ int moe_b200_grouped_gemm_down(const void* h_sorted, int rows_cap, const void* w
   a.sorted_ids = sorted_token_ids; a.expert_ids = expert_ids; a.num_post_pad = num_tokens_post_pad;
   a.numel = T * top_k; a.top_k = top_k; a.max_m_blocks = rows_cap / kBlockM; a.num_experts = E;
   a.hidden = H; a.inter = I; a.activation = 0; a.status = status_word;
-  return launch_grouped_gemm2(a, static_cast<const __nv_bfloat16*>(h_sorted), rows_cap,
-                              static_cast<const __nv_bfloat16*>(w2), static_cast<const __nv_bfloat16*>(w2_bias),
-                              topk_weights, static_cast<__nv_bfloat16*>(c3), static_cast<cudaStream_t>(stream));
-}
-
-size_t moe_b200_combine_counter_bytes(int T, int H) {
-  if (T < 0 || H <= 0) return 0;
-  return sizeof(int) * static_cast<size_t>(combine_counter_ints(T > 0 ? T : 1, H));
-}
-
-int moe_b200_grouped_gemm_down_combine(const void* h_sorted, int rows_cap, const void* w2, const void* w2_bias,
-                                       const float* topk_weights, const int32_t* sorted_token_ids,
-                                       const int32_t* expert_ids, const int32_t* num_tokens_post_pad, void* c3,
-                                       void* out, int32_t* counters, int T, int E, int top_k, int H, int I,
-                                       int32_t* status_word, void* stream) {
-  if (int st = check_block_shapes(T, E, top_k, H, I)) return st;
-  if (h_sorted == nullptr || w2 == nullptr || topk_weights == nullptr || sorted_token_ids == nullptr ||
-      expert_ids == nullptr || num_tokens_post_pad == nullptr || c3 == nullptr || out == nullptr ||
-      counters == nullptr || status_word == nullptr)
-    return set_error(kStatusInvalidArgument, "grouped_gemm_down_combine: null pointer");
-  if (rows_cap % kBlockM != 0) return set_error(kStatusInvalidArgument, "grouped_gemm_down_combine: rows_cap must be a multiple of %d", kBlockM);
-  GroupedGemmArgs a{};
-  a.sorted_ids = sorted_token_ids; a.expert_ids = expert_ids; a.num_post_pad = num_tokens_post_pad;
-  a.numel = T * top_k; a.top_k = top_k; a.max_m_blocks = rows_cap / kBlockM; a.num_experts = E;
-  a.hidden = H; a.inter = I; a.activation = 0; a.status = status_word;
-  a.combine_counters = counters; a.combine_out = static_cast<__nv_bfloat16*>(out);
   return launch_grouped_gemm2(a, static_cast<const __nv_bfloat16*>(h_sorted), rows_cap,
                               static_cast<const __nv_bfloat16*>(w2), static_cast<const __nv_bfloat16*>(w2_bias),
                               topk_weights, static_cast<__nv_bfloat16*>(c3), static_cast<cudaStream_t>(stream));
@@ -334,8 +300,11 @@ int moe_b200_fused_experts(const void* x, const void* w13, const void* w2, const
   if (workspace == nullptr || workspace_bytes < need)
     return set_error(kStatusWorkspaceTooSmall, "fused_experts: workspace of %zu bytes needed, %zu given", need, workspace_bytes);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  return run_experts(x, w13, w2, w13_bias, w2_bias, topk_weights, topk_ids, T, E, top_k, H, I, activation,
-                     carve_experts(workspace, T, E, top_k, H, I), out, status_word, s);
+  if (int st = run_experts_until_c3_ws(x, w13, w2, w13_bias, w2_bias, topk_weights, topk_ids, T, E, top_k, H, I,
+                                       activation, workspace, status_word, s))
+    return st;
+  return launch_moe_sum(experts_workspace_c3(workspace, T, E, top_k, H, I), static_cast<__nv_bfloat16*>(out), T, top_k,
+                        H, s);
 }
 
 int moe_b200_rms_norm(void* out, const void* input, const void* weight, float eps, int T, int H, void* stream) {
@@ -512,14 +481,11 @@ int moe_b200_fused_moe_forward_tp(const void* x, const void* router_logits, int 
   int32_t* ti = reinterpret_cast<int32_t*>(base + slot);
   if (int st = launch_topk_softmax(router_logits, logits_is_bf16, tw, ti, nullptr, T, E, top_k, renormalize, s)) return st;
   void* ews = base + 2 * slot;
-  const __nv_bfloat16* partial = nullptr;
-  if (int st = run_experts_partial_ws(x, w13, w2, w13_bias, w2_bias, tw, ti, T, E, top_k, H, I, activation, ews,
-                                      status_word, s, &partial))
+  if (int st = run_experts_until_c3_ws(x, w13, w2, w13_bias, w2_bias, tw, ti, T, E, top_k, H, I, activation, ews,
+                                       status_word, s))
     return st;
-  // the k slots are already combined: the reduction's first phase only moves this rank's [T, H] partial sum into
-  // its peer-visible buffer (k = 1)
-  return ar_moe_sum_all_reduce_impl(ar_handle, partial, out, T, 1, H, reg_buffer, reg_buffer_bytes, ar_algo,
-                                    status_word, s);
+  return ar_moe_sum_all_reduce_impl(ar_handle, experts_workspace_c3(ews, T, E, top_k, H, I), out, T, top_k, H,
+                                    reg_buffer, reg_buffer_bytes, ar_algo, status_word, s);
 }
 
 int moe_b200_fused_moe_forward_tp_add_rms_norm(const void* x, const void* router_logits, int logits_is_bf16,
@@ -546,11 +512,10 @@ int moe_b200_fused_moe_forward_tp_add_rms_norm(const void* x, const void* router
   int32_t* ti = reinterpret_cast<int32_t*>(base + slot);
   if (int st = launch_topk_softmax(router_logits, logits_is_bf16, tw, ti, nullptr, T, E, top_k, renormalize, s)) return st;
   void* ews = base + 2 * slot;
-  const __nv_bfloat16* partial = nullptr;
-  if (int st = run_experts_partial_ws(x, w13, w2, w13_bias, w2_bias, tw, ti, T, E, top_k, H, I, activation, ews,
-                                      status_word, s, &partial))
+  if (int st = run_experts_until_c3_ws(x, w13, w2, w13_bias, w2_bias, tw, ti, T, E, top_k, H, I, activation, ews,
+                                       status_word, s))
     return st;
-  return ar_all_reduce_add_rms_norm_impl(ar_handle, partial, 1, scratch_out,
+  return ar_all_reduce_add_rms_norm_impl(ar_handle, experts_workspace_c3(ews, T, E, top_k, H, I), top_k, scratch_out,
                                          static_cast<__nv_bfloat16*>(residual), static_cast<const __nv_bfloat16*>(norm_weight),
                                          eps, static_cast<__nv_bfloat16*>(normed_out), T, H, reg_buffer, reg_buffer_bytes,
                                          ar_algo, status_word, s);

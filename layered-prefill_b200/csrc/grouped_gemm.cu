@@ -11,10 +11,15 @@
 //     into a shared-memory ring that takes all 227 KB (4 stages at N=256, 5 at N=192, 7 at N=128); the
 //     token rows (hidden states gathered through the permutation in pass 1, rows of the permuted
 //     intermediate in pass 2) come in with 16-byte cp.async from four warps, written straight into the
-//     same swizzled K-major layout; a stage is handed to the tensor core one stage late, after its copies
-//     completed and a fence.proxy.async (generic-proxy writes before async-proxy reads, CpAsyncStageHandOff
-//     in ptx.cuh). Splitting the operands over the TMA unit and the LSU path measured faster than TMA for
-//     both, and padding rows cost no traffic (zero-fill);
+//     same swizzled K-major layout, and signal the stage's barrier asynchronously
+//     (cp.async.mbarrier.arrive.noinc: the arrival fires when the thread's copies have landed), which is how
+//     CUTLASS's sm_100 collectives hand cp.async-filled stages to tcgen05.mma
+//     (cutlass/gemm/collective/sm100_mma_cpasync_warpspecialized.hpp, ..._mixed_tma_cpasync_...: producer_commit
+//     with cpasync_barrier_arrive, consumer_wait, UMMA, no proxy fence in between). A variant that waited for
+//     the copies (cp.async.wait_group), issued fence.proxy.async and arrived one stage late measured 5 % slower
+//     at decode and 10 % at prefill (the gather thread then keeps two stages in flight instead of the whole
+//     ring) with bit-identical results, and was not kept. Splitting the operands over the TMA unit and the LSU
+//     path measured faster than TMA for both, and padding rows cost no traffic (zero-fill);
 //   * one thread issues tcgen05.mma (M=128, N<=256, K=16 per instruction) into one of two 256-column
 //     TMEM accumulators, so the epilogue of tile i overlaps the main loop of tile i+1;
 //   * pass 1 keeps the gate rows and the matching up rows of w13 in the same tile (columns [0,BNH)
@@ -76,12 +81,6 @@ struct KernelParams {
   int* status;
   int stages;       // ring depth (2..kMaxStages)
   int stage_bytes;  // kABytes + mma_n * 128
-  // top-k combine inside the down pass (null: the slot rows are the only output)
-  int* combine_cnt;            // [T, n_tiles] arrival counters, zero when the down pass starts
-  __nv_bfloat16* combine_out;  // [T, out_cols]: bf16(sum over the k slot rows), written by the last arriver
-  // gate_up pass: words to clear for the pass that follows (the combine counters)
-  int* zero_ptr;
-  int zero_count;
 };
 
 union Pack8 {
@@ -197,46 +196,6 @@ __device__ __forceinline__ void epilogue_rows(const KernelParams& p, uint32_t ta
       }
       __syncwarp();  // the patch is rewritten by the next 64 columns
     }
-    if (p.combine_out != nullptr) {
-      // Top-k combine (the reference's moe_sum, nanovllm/layers/for_moe/fused_moe.py:630-631) without a further
-      // pass: every slot row counts its arrival per (token, column tile); whoever brings the count to top_k
-      // finds all k rows of that token complete, adds them in slot order in fp32 and writes the bf16 result, so
-      // the value does not depend on which slot came last. Writer side: stores, device-scope fence, then the
-      // count; reader side: count, fence, loads from L2.
-      __threadfence();
-      __syncwarp();
-      const int n_tile = n0 / p.tile_cols;
-      bool last = false;
-      int* cnt = nullptr;
-      if (flat < p.numel) {
-        cnt = p.combine_cnt + static_cast<long long>(flat / p.top_k) * p.n_tiles + n_tile;
-        last = atomicAdd(cnt, 1) == p.top_k - 1;
-      }
-      unsigned pending = __ballot_sync(0xffffffffu, last);
-      if (pending != 0u) __threadfence();
-      if (last) *cnt = 0;  // left clean for the next pass over this workspace
-      while (pending != 0u) {
-        const int r = __ffs(pending) - 1;
-        pending &= pending - 1u;
-        const long long t = __shfl_sync(0xffffffffu, flat, r) / p.top_k;
-        for (int c = lane * 8; c < p.tile_cols; c += 256) {
-          const int col = n0 + c;
-          if (col >= p.out_cols) break;
-          float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-          const __nv_bfloat16* src = p.out + t * p.top_k * p.out_ld + col;
-          for (int j = 0; j < p.top_k; ++j) {
-            Pack8 v;
-            v.u = __ldcg(reinterpret_cast<const uint4*>(src + static_cast<long long>(j) * p.out_ld));
-#pragma unroll
-            for (int q8 = 0; q8 < 8; ++q8) acc[q8] += __bfloat162float(v.h[q8]);
-          }
-          Pack8 o;
-#pragma unroll
-          for (int q8 = 0; q8 < 8; ++q8) o.h[q8] = __float2bfloat16_rn(acc[q8]);
-          *reinterpret_cast<uint4*>(p.combine_out + t * p.out_ld + col) = o.u;
-        }
-      }
-    }
   }
 }
 
@@ -282,10 +241,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b, const KernelPara
   grid_dependency_launch();
   grid_dependency_wait();
 
-  if (kMode == 1 && p.zero_ptr != nullptr) {
-    // the previous pass over this workspace is complete (dependency wait above), the next one has not begun
-    for (int i = blockIdx.x * kThreads + threadIdx.x; i < p.zero_count; i += gridDim.x * kThreads) p.zero_ptr[i] = 0;
-  }
   const int num_m_blocks = *p.num_post_pad / BM;
   const int total_tiles = num_m_blocks * p.n_tiles;
   const int num_kb = (p.K + BK - 1) / BK;
@@ -422,7 +377,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b, const KernelPara
     const int ch = lane & 7;             // 16-byte chunk inside the 128-byte row
     const int row0 = gw * 4 + sub;       // rows handled: row0 + 16*i
     const uint32_t swz = static_cast<uint32_t>((ch ^ (row0 & 7)) << 4);
-    CpAsyncStageHandOff hand_off;
     uint32_t s = 0, ph = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
@@ -437,14 +391,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b, const KernelPara
           src[i] = flat < p.numel ? p.x + (static_cast<long long>(m_blk) * BM + row0 + 16 * i) * p.K + ch * 8 : nullptr;
       }
       for (int kb = 0; kb < num_kb; ++kb) {
-        if (!__all_sync(0xffffffffu, mbar_try_wait(&bar_empty[s], ph ^ 1u))) {
-          hand_off.flush();  // the ring is full: nothing to overlap with, publish the outstanding stage first
-          ok = mbar_wait(&bar_empty[s], ph ^ 1u);
-          ok = __all_sync(0xffffffffu, ok);
-          if (!ok) {
-            if (lane == 0) report(p.status, kErrWaitEmpty);
-            break;
-          }
+        ok = mbar_wait(&bar_empty[s], ph ^ 1u);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) {
+          if (lane == 0) report(p.status, kErrWaitEmpty);
+          break;
         }
         const uint32_t a_base = smem_u32(ring + s * stage_bytes);
         const bool in_k = kb * BK + ch * 8 < p.K;
@@ -455,14 +406,15 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b, const KernelPara
           cp_async_16(dst, live ? static_cast<const void*>(src[i] + kb * BK) : static_cast<const void*>(p.x),
                       live ? 16u : 0u);
         }
-        hand_off.issued(&bar_full[s]);
+        // the stage's barrier counts this thread as arrived once the copies above have landed
+        cp_async_mbar_arrive_noinc(&bar_full[s]);
         if (++s == num_stages) {
           s = 0;
           ph ^= 1u;
         }
       }
     }
-    hand_off.flush();
+    cp_async_wait_all();
   }
 
   tc_fence_before_sync();
@@ -582,10 +534,6 @@ double wave_efficiency(double tiles, int sms) {
   return waves > 0 ? tiles / (waves * sms) : 1.0;
 }
 
-// Arrival counters of the top-k combine: one per token and 128-column tile of the hidden dimension (the down pass
-// uses 128- or 256-column tiles, or a single tile when hidden <= 128).
-int combine_counter_ints(int tokens, int hidden) { return tokens * (hidden <= 128 ? 1 : (hidden + 127) / 128); }
-
 int device_sm_count() {
   static int cached[64] = {0};
   int dev = 0;
@@ -618,8 +566,6 @@ int launch_grouped_gemm1(const GroupedGemmArgs& a, const __nv_bfloat16* x, const
   p.interleaved = a.activation == 1 ? 1 : 0;
   p.out = h_sorted; p.out_ld = a.inter; p.topk_w = nullptr; p.bias = w13_bias;
   p.alpha = a.act_alpha; p.limit = a.act_limit; p.status = a.status;
-  p.zero_ptr = a.combine_counters;
-  p.zero_count = a.combine_counters != nullptr ? combine_counter_ints(a.numel / a.top_k, a.hidden) : 0;
   pick_ring(mma_n, 0, &p.stages, &p.stage_bytes);
   (void)rows_cap;
 
@@ -655,12 +601,6 @@ int launch_grouped_gemm2(const GroupedGemmArgs& a, const __nv_bfloat16* h_sorted
   p.out_cols = a.hidden; p.inter = a.inter; p.interleaved = 0;
   p.out = c3; p.out_ld = a.hidden; p.topk_w = topk_w; p.bias = w2_bias;
   p.alpha = 0.f; p.limit = 0.f; p.status = a.status;
-  if ((a.combine_out != nullptr) != (a.combine_counters != nullptr))
-    return set_error(kStatusInvalidArgument, "grouped GEMM down: the combine needs both its output and its counters");
-  if (a.combine_out != nullptr && p.n_tiles > combine_counter_ints(1, a.hidden))
-    return set_error(kStatusInvalidArgument, "grouped GEMM down: more column tiles than combine counters per token");
-  p.combine_cnt = a.combine_counters;
-  p.combine_out = a.combine_out;
   pick_ring(p.mma_n, 4 * kPatchBytes, &p.stages, &p.stage_bytes);
 
   long long tiles = static_cast<long long>(a.max_m_blocks) * p.n_tiles;

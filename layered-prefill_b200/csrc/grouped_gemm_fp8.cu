@@ -315,7 +315,6 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_b, const Params
     const int ch = lane & 7;
     const int row0 = gw * 4 + sub;
     const uint32_t swz = static_cast<uint32_t>((ch ^ (row0 & 7)) << 4);
-    CpAsyncStageHandOff hand_off;
     uint32_t s = 0, ph = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
@@ -331,14 +330,11 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_b, const Params
           src[i] = flat < p.numel ? p.a_q + pos * p.K : nullptr;
       }
       for (int kb = 0; kb < num_kb; ++kb) {
-        if (!__all_sync(0xffffffffu, mbar_try_wait(&bar_empty[s], ph ^ 1u))) {
-          hand_off.flush();  // the ring is full: nothing to overlap with, publish the outstanding stage first
-          ok = mbar_wait(&bar_empty[s], ph ^ 1u);
-          ok = __all_sync(0xffffffffu, ok);
-          if (!ok) {
-            if (lane == 0) report(p.status, kErrWaitEmpty);
-            break;
-          }
+        ok = mbar_wait(&bar_empty[s], ph ^ 1u);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) {
+          if (lane == 0) report(p.status, kErrWaitEmpty);
+          break;
         }
         const uint32_t a_base = smem_u32(ring + s * kStageBytes);
         const int col = kb * kGroup - p.k_shift + ch * 16;  // this lane's 16 columns of the stage, in the rank's K range
@@ -349,14 +345,15 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_b, const Params
           const bool live = in_k && src[i] != nullptr;
           cp_async_16(dst, live ? static_cast<const void*>(src[i] + col) : static_cast<const void*>(p.a_q), live ? 16u : 0u);
         }
-        hand_off.issued(&bar_full[s]);
+        // the stage's barrier counts this thread as arrived once the copies above have landed
+        cp_async_mbar_arrive_noinc(&bar_full[s]);
         if (++s == kStages) {
           s = 0;
           ph ^= 1u;
         }
       }
     }
-    hand_off.flush();
+    cp_async_wait_all();
   }
 
   tc_fence_before_sync();

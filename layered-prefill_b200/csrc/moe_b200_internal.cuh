@@ -69,13 +69,7 @@ struct GroupedGemmArgs {
   int activation;   // 0 silu, 1 swigluoai (interleaved gate/up)
   float act_alpha, act_limit;
   int* status;      // device status word (0 = ok)
-  // top-k combine fused into the down pass (both null: the down pass only writes the slot rows c3[t*k+j]).
-  // combine_counters: combine_counter_ints(T, hidden) ints, all zero when the down pass starts; the gate_up pass
-  // given the same pointer clears them, and the down pass leaves them zero. combine_out: bf16 [T, hidden].
-  int* combine_counters;
-  __nv_bfloat16* combine_out;
 };
-int combine_counter_ints(int tokens, int hidden);
 // h_sorted[p, :] = act(x[sorted_ids[p] / top_k] @ w13[e]^T), p in permuted order, bf16 [rows_cap, inter]
 int launch_grouped_gemm1(const GroupedGemmArgs& a, const __nv_bfloat16* x, const __nv_bfloat16* w13,
                          const __nv_bfloat16* w13_bias, __nv_bfloat16* h_sorted, int rows_cap, cudaStream_t stream);

@@ -131,35 +131,6 @@ __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
-// Hands shared-memory stages that this thread filled with non-bulk cp.async copies over to the tensor core.
-// Those copies write shared memory through the generic proxy while tcgen05.mma reads its operands through the
-// async proxy, so a stage is published in this order: its copies are complete (cp.async.wait_group), a
-// fence.proxy.async orders them before later async-proxy reads, and only then the thread arrives on the stage's
-// barrier (a plain arrive; the barrier's count includes it). To keep the copies of two stages in flight, a stage
-// is published after the copies of the next one were issued; flush() publishes the outstanding stage at once
-// (before blocking on a full ring, and at the end).
-struct CpAsyncStageHandOff {
-  uint64_t* pending = nullptr;
-  __device__ __forceinline__ void flush() {
-    if (pending != nullptr) {
-      cp_async_wait<0>();
-      fence_proxy_async_smem();
-      mbar_arrive(pending);
-      pending = nullptr;
-    }
-  }
-  // Call right after issuing the copies of the stage whose barrier is `bar`.
-  __device__ __forceinline__ void issued(uint64_t* bar) {
-    cp_async_commit();
-    if (pending != nullptr) {
-      cp_async_wait<1>();
-      fence_proxy_async_smem();
-      mbar_arrive(pending);
-    }
-    pending = bar;
-  }
-};
-
 // ---------------------------------------------------------------- tcgen05: TMEM management
 __device__ __forceinline__ void tmem_alloc(uint32_t* smem_out, uint32_t ncols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_out)),

@@ -102,34 +102,55 @@ class FusedMoE(torch.nn.Module):
     # ------------------------------------------------------------------ checkpoint -> parameter
     def weight_loader(self, param: torch.nn.Parameter, loaded_weight: torch.Tensor, weight_name: str, shard_id: str,
                       expert_id: int, return_success: bool = False) -> Optional[bool]:
-        """nanovllm/layers/fused_moe.py:472-658 for model weights and biases: gate rows ("w1") fill the
-        first half of w13[e], up rows ("w3") the second half, each narrowed to this rank's slice of I
-        (:398-414); down ("w2") is narrowed on its input dimension (:416-432); w2_bias lives on rank 0 only
-        and w13_bias is sliced like its weight (:647-654)."""
-        if shard_id not in ("w1", "w2", "w3"):
-            raise ValueError(f"shard_id must be ['w1','w2','w3'] but got {shard_id}.")
-        tp_rank = self.tp_rank
+        """nanovllm/layers/fused_moe.py:472-658, the cases an unquantised layer meets (what utils/loader.py:37-93
+        feeds it):
+          * per-expert 2-D tensors, "weight" in the name: gate rows ("w1") fill the first half of w13[e], up rows
+            ("w3") the second half, each narrowed to this rank's slice of I (:398-414); down ("w2") is narrowed on
+            its input dimension (:416-432);
+          * all-expert 3-D tensors (gpt-oss: "gate_up_proj_blocks" / "down_proj_blocks" after dequantisation), shard
+            "w13": rows [rank * 2I/tp, (rank+1) * 2I/tp) of the fused, interleaved gate_up rows (:388-392); "w2":
+            this rank's slice of the last dimension;
+          * biases come as all-expert tensors too: "w2" is copied on rank 0 only, anything else is this rank's
+            contiguous slice of the last dimension (:647-654);
+          * shard "all": the whole parameter at once (:479-487)."""
+        if shard_id == "all":
+            if "bias" in weight_name:
+                param.data.copy_(loaded_weight)
+            else:
+                param.data.copy_(loaded_weight.reshape(*param.data.shape[:-1], -1))
+            return True if return_success else None
+        if shard_id not in ("w1", "w2", "w3", "all", "w13"):
+            raise ValueError(f"shard_id must be ['w1','w2','w3', 'all'] but got {shard_id}.")
+        tp_rank, tp_size = self.tp_rank, self.tp_size
+        full_load = loaded_weight.dim() == 3 or "bias" in weight_name or "block" in weight_name
+        expert_data = param.data if full_load else param.data[expert_id]
+        if "weight" in weight_name or "block" in weight_name:
+            if "weight" in weight_name:
+                shard_dim = {"w1": 0, "w2": 1, "w3": 0, "w13": 1}[shard_id] + (1 if full_load else 0)
+            else:
+                shard_dim = -1
+            if expert_data.dim() != loaded_weight.dim():
+                loaded_weight = loaded_weight.reshape(*loaded_weight.shape[:-2], -1)
+            if shard_id == "w2":
+                shard = expert_data.shape[shard_dim]
+                expert_data.copy_(loaded_weight.narrow(shard_dim, shard * tp_rank, shard))
+            elif shard_id in ("w1", "w3"):
+                shard = expert_data.shape[shard_dim] // 2
+                sl = loaded_weight.narrow(shard_dim, shard * tp_rank, shard)
+                expert_data.narrow(shard_dim, 0 if shard_id == "w1" else shard, shard).copy_(sl)
+            else:  # "w13": the fused gate_up rows, sharded on the output dimension
+                shard = expert_data.shape[1]
+                expert_data.narrow(1, 0, shard).copy_(loaded_weight.narrow(1, shard * tp_rank, shard))
+            return True if return_success else None
         if "bias" in weight_name:
-            expert_data = param.data[expert_id]
             if shard_id == "w2":
                 if tp_rank == 0:
                     expert_data.copy_(loaded_weight)
             else:
-                shard = expert_data.shape[0] // 2
-                sl = loaded_weight.narrow(0, shard * tp_rank, shard)
-                expert_data.narrow(0, 0 if shard_id == "w1" else shard, shard).copy_(sl)
+                n = loaded_weight.size(-1)
+                expert_data.copy_(loaded_weight.narrow(-1, tp_rank * n // tp_size, n // tp_size))
             return True if return_success else None
-        if "weight" not in weight_name:
-            raise ValueError(f"Unrecognized weight_name {weight_name}.")
-        expert_data = param.data[expert_id]
-        if shard_id == "w2":
-            shard = expert_data.shape[1]
-            expert_data.copy_(loaded_weight.narrow(1, shard * tp_rank, shard))
-        else:
-            shard = expert_data.shape[0] // 2
-            sl = loaded_weight.narrow(0, shard * tp_rank, shard)
-            expert_data.narrow(0, 0 if shard_id == "w1" else shard, shard).copy_(sl)
-        return True if return_success else None
+        raise ValueError(f"Unrecognized weight_name {weight_name}.")
 
     @classmethod
     def make_expert_params_mapping(cls, ckpt_gate_proj_name: str, ckpt_down_proj_name: str, ckpt_up_proj_name: str,

@@ -263,14 +263,18 @@ def test_fused_moe_module_forward_single_gpu(activation, bias):
     w2 = (torch.randn(E, H, I, generator=g) * scale).to(torch.bfloat16)
     b13 = (torch.randn(E, 2 * I, generator=g) * 0.1).to(torch.bfloat16) if bias else None
     b2 = (torch.randn(E, H, generator=g) * 0.1).to(torch.bfloat16) if bias else None
-    for e in range(E):
-        layer.weight_loader(layer.w13_weight, w13[e, :I].to(d), "experts.w13_weight", "w1", e)
-        layer.weight_loader(layer.w13_weight, w13[e, I:].to(d), "experts.w13_weight", "w3", e)
-        layer.weight_loader(layer.w2_weight, w2[e].to(d), "experts.w2_weight", "w2", e)
-        if bias:
-            layer.weight_loader(layer.w13_bias, b13[e, :I].to(d), "experts.w13_bias", "w1", e)
-            layer.weight_loader(layer.w13_bias, b13[e, I:].to(d), "experts.w13_bias", "w3", e)
-            layer.weight_loader(layer.w2_bias, b2[e].to(d), "experts.w2_bias", "w2", e)
+    if activation == "swigluoai":  # gpt-oss checkpoints: fused all-expert tensors (utils/loader.py:41-49)
+        layer.weight_loader(layer.w13_weight, w13.to(d), "experts.gate_up_proj_blocks", "w13", 0)
+        layer.weight_loader(layer.w2_weight, w2.to(d), "experts.down_proj_blocks", "w2", 0)
+    else:
+        for e in range(E):
+            layer.weight_loader(layer.w13_weight, w13[e, :I].to(d), "experts.w13_weight", "w1", e)
+            layer.weight_loader(layer.w13_weight, w13[e, I:].to(d), "experts.w13_weight", "w3", e)
+            layer.weight_loader(layer.w2_weight, w2[e].to(d), "experts.w2_weight", "w2", e)
+    if bias:  # biases always come as all-expert tensors (layers/fused_moe.py:647-654)
+        layer.weight_loader(layer.w13_bias, b13.to(d), "experts.gate_up_proj_bias", "w13", 0)
+        layer.weight_loader(layer.w2_bias, b2.to(d), "experts.down_proj_bias", "w2", 0)
+        assert torch.equal(layer.w13_bias.cpu(), b13) and torch.equal(layer.w2_bias.cpu(), b2)
     assert torch.equal(layer.w13_weight.cpu(), w13) and torch.equal(layer.w2_weight.cpu(), w2)
     x = torch.randn(T, H, generator=g).to(torch.bfloat16)
     logits = torch.randn(T, E, generator=g).to(torch.bfloat16)
@@ -288,45 +292,3 @@ def test_fused_moe_module_forward_single_gpu(activation, bias):
     assert torch.equal(sti.cpu(), ti) and torch.allclose(stw.cpu(), tw, rtol=1e-6, atol=1e-8)
     # maybe_all_reduce on one rank is the identity
     assert layer.maybe_all_reduce_tensor_model_parallel(out) is out
-
-
-@pytest.mark.parametrize("T,H,E,k,I", [(64, 2048, 128, 8, 96), (700, 320, 8, 4, 64), (2048, 1024, 16, 8, 128), (5, 64, 4, 2, 16)])
-def test_down_pass_with_combine_equals_down_pass_then_moe_sum(T, H, E, k, I):
-    """The top-k combine inside the down pass (last-arriving slot of a token adds the k rows in slot order) must give
-    the bits of the separate k-slot sum, on every call: the arrival counters are left clean."""
-    from layered_prefill_b200 import fused_moe, ops
-    from layered_prefill_b200._lib import check, lib
-    d = _dev()
-    g = torch.Generator().manual_seed(T + H)
-    x = torch.randn(T, H, generator=g).to(torch.bfloat16).to(d)
-    w13 = (torch.randn(E, 2 * I, H, generator=g) * 0.05).to(torch.bfloat16).to(d)
-    w2 = (torch.randn(E, H, I, generator=g) * 0.05).to(torch.bfloat16).to(d)
-    logits = (torch.randn(T, E, generator=g) + 2.0 * torch.randn(E, generator=g)).to(d)
-    tw, ti, _ = fused_moe.fused_topk(x, logits, k, True)
-    bm = lib.moe_b200_block_m()
-    s_ids, e_ids, post = fused_moe.moe_align_block_size(ti, bm, E)
-    rows_cap = (s_ids.numel() + bm - 1) // bm * bm
-    s_pad = torch.full((rows_cap,), T * k, dtype=torch.int32, device=d)
-    s_pad[:s_ids.numel()] = s_ids
-    h = torch.zeros(rows_cap, I, dtype=torch.bfloat16, device=d)
-    stw = ops.status_word(d).data_ptr()
-    stream = torch.cuda.current_stream().cuda_stream
-    check(lib.moe_b200_grouped_gemm_gate_up(x.data_ptr(), w13.data_ptr(), 0, s_pad.data_ptr(), e_ids.data_ptr(),
-                                            post.data_ptr(), h.data_ptr(), rows_cap, T, E, k, H, I, 0, stw, stream))
-    c3_a = torch.empty(T * k, H, dtype=torch.bfloat16, device=d)
-    check(lib.moe_b200_grouped_gemm_down(h.data_ptr(), rows_cap, w2.data_ptr(), 0, tw.data_ptr(), s_pad.data_ptr(),
-                                         e_ids.data_ptr(), post.data_ptr(), c3_a.data_ptr(), T, E, k, H, I, stw, stream))
-    want = torch.empty(T, H, dtype=torch.bfloat16, device=d)
-    ops.moe_sum(c3_a.view(T, k, H), want)
-    counters = torch.zeros(lib.moe_b200_combine_counter_bytes(T, H) // 4, dtype=torch.int32, device=d)
-    for rep in range(3):
-        c3_b = torch.empty(T * k, H, dtype=torch.bfloat16, device=d)
-        got = torch.full((T, H), float("nan"), dtype=torch.bfloat16, device=d)
-        check(lib.moe_b200_grouped_gemm_down_combine(
-            h.data_ptr(), rows_cap, w2.data_ptr(), 0, tw.data_ptr(), s_pad.data_ptr(), e_ids.data_ptr(), post.data_ptr(),
-            c3_b.data_ptr(), got.data_ptr(), counters.data_ptr(), T, E, k, H, I, stw, stream))
-        torch.cuda.synchronize()
-        assert torch.equal(c3_a, c3_b), f"slot rows differ (call {rep})"
-        assert torch.equal(got, want), f"combined rows differ from moe_sum (call {rep})"
-        assert int(counters.abs().sum()) == 0, "arrival counters were not left clean"
-    _check_status()

@@ -122,27 +122,34 @@ def test_variants_against_reference(ref, T, H, E, k, I, activation, bias):
     _bounds(want, rout.cpu(), "oracle vs reference", scaled=True)
 
 
-def _fill_through_loaders(layers, E, I, H, bias, seed):
-    """Checkpoint-shaped tensors (per expert gate / up / down) pushed through every layer's own weight_loader."""
+def _fill_through_loaders(layers, E, I, H, bias, seed, fused=False):
+    """Checkpoint-shaped tensors pushed through every layer's own weight_loader, as utils/loader.py:37-93 calls it:
+    per expert gate / up / down (Qwen3-MoE), or all-expert fused tensors and biases (gpt-oss, fused=True)."""
     g = torch.Generator().manual_seed(seed)
-    for e in range(E):
-        gate = (torch.randn(I, H, generator=g) * 0.05).to(torch.bfloat16)
-        up = (torch.randn(I, H, generator=g) * 0.05).to(torch.bfloat16)
-        down = (torch.randn(H, I, generator=g) * 0.05).to(torch.bfloat16)
+    if fused:
+        gate_up = (torch.randn(E, 2 * I, H, generator=g) * 0.05).to(torch.bfloat16)
+        down = (torch.randn(E, H, I, generator=g) * 0.05).to(torch.bfloat16)
         for m in layers:
             dev = m.w13_weight.device
-            m.weight_loader(m.w13_weight, gate.to(dev), "experts.w13_weight", "w1", e)
-            m.weight_loader(m.w13_weight, up.to(dev), "experts.w13_weight", "w3", e)
-            m.weight_loader(m.w2_weight, down.to(dev), "experts.w2_weight", "w2", e)
-        if bias:
-            bg = (torch.randn(I, generator=g) * 0.1).to(torch.bfloat16)
-            bu = (torch.randn(I, generator=g) * 0.1).to(torch.bfloat16)
-            bd = (torch.randn(H, generator=g) * 0.1).to(torch.bfloat16)
+            m.weight_loader(m.w13_weight, gate_up.to(dev), "model.layers.0.mlp.experts.gate_up_proj_blocks", "w13", 0)
+            m.weight_loader(m.w2_weight, down.to(dev), "model.layers.0.mlp.experts.down_proj_blocks", "w2", 0)
+    else:
+        for e in range(E):
+            gate = (torch.randn(I, H, generator=g) * 0.05).to(torch.bfloat16)
+            up = (torch.randn(I, H, generator=g) * 0.05).to(torch.bfloat16)
+            down = (torch.randn(H, I, generator=g) * 0.05).to(torch.bfloat16)
             for m in layers:
                 dev = m.w13_weight.device
-                m.weight_loader(m.w13_bias, bg.to(dev), "experts.w13_bias", "w1", e)
-                m.weight_loader(m.w13_bias, bu.to(dev), "experts.w13_bias", "w3", e)
-                m.weight_loader(m.w2_bias, bd.to(dev), "experts.w2_bias", "w2", e)
+                m.weight_loader(m.w13_weight, gate.to(dev), "experts.w13_weight", "w1", e)
+                m.weight_loader(m.w13_weight, up.to(dev), "experts.w13_weight", "w3", e)
+                m.weight_loader(m.w2_weight, down.to(dev), "experts.w2_weight", "w2", e)
+    if bias:
+        b13 = (torch.randn(E, 2 * I, generator=g) * 0.1).to(torch.bfloat16)
+        b2 = (torch.randn(E, H, generator=g) * 0.1).to(torch.bfloat16)
+        for m in layers:
+            dev = m.w13_weight.device
+            m.weight_loader(m.w13_bias, b13.to(dev), "model.layers.0.mlp.experts.gate_up_proj_bias", "w13", 0)
+            m.weight_loader(m.w2_bias, b2.to(dev), "model.layers.0.mlp.experts.down_proj_bias", "w2", 0)
 
 
 @pytest.mark.parametrize("activation,bias", [("silu", False), ("swigluoai", True)])
@@ -156,8 +163,10 @@ def test_fused_moe_layer_against_reference_layer(ref, single_rank_group, activat
               reduce_results=False, renormalize=True, activation=activation, has_bias=bias)
     with torch.device(d):
         rm, om = rlayer.FusedMoE(**kw), olayer.FusedMoE(**kw)
-    _fill_through_loaders([rm, om], E, I, H, bias, seed=5)
+    _fill_through_loaders([rm, om], E, I, H, bias, seed=5, fused=activation == "swigluoai")
     assert torch.equal(rm.w13_weight, om.w13_weight) and torch.equal(rm.w2_weight, om.w2_weight)
+    if bias:
+        assert torch.equal(rm.w13_bias, om.w13_bias) and torch.equal(rm.w2_bias, om.w2_bias)
     g = torch.Generator().manual_seed(9)
     x = torch.randn(T, H, generator=g).to(torch.bfloat16).to(d)
     lg = torch.randn(T, E, generator=g).to(torch.bfloat16).to(d)

@@ -37,29 +37,44 @@ def _worker(rank, world, port, q):
         b2 = torch.randn(E, H, generator=g).to(torch.bfloat16)
         logits = torch.randn(T, E, generator=g)
 
-        layer = FusedMoE(E, k, H, I, params_dtype=torch.bfloat16, has_bias=True)
+        layer = FusedMoE(E, k, H, I, params_dtype=torch.bfloat16)
         assert (layer.tp_size, layer.tp_rank) == (world, rank)
         assert layer.w13_weight.shape == (E, 2 * I // world, H) and layer.w2_weight.shape == (E, H, I // world)
-        for e in range(E):
+        for e in range(E):  # Qwen3-MoE checkpoints: one tensor per expert and projection
             layer.weight_loader(layer.w13_weight, w13[e, :I], "model.layers.0.mlp.experts.0.gate_proj.weight", "w1", e)
             layer.weight_loader(layer.w13_weight, w13[e, I:], "model.layers.0.mlp.experts.0.up_proj.weight", "w3", e)
             layer.weight_loader(layer.w2_weight, w2[e], "model.layers.0.mlp.experts.0.down_proj.weight", "w2", e)
-            layer.weight_loader(layer.w13_bias, b13[e, :I], "experts.gate_proj.bias", "w1", e)
-            layer.weight_loader(layer.w13_bias, b13[e, I:], "experts.up_proj.bias", "w3", e)
-            layer.weight_loader(layer.w2_bias, b2[e], "experts.down_proj.bias", "w2", e)
         sh13, sh2 = O.shard_expert_weights(w13, w2, world, rank)
         assert torch.equal(layer.w13_weight.data, sh13) and torch.equal(layer.w2_weight.data, sh2)
         ip = I // world
-        assert torch.equal(layer.w13_bias.data[:, :ip], b13[:, rank * ip:(rank + 1) * ip])
-        assert torch.equal(layer.w13_bias.data[:, ip:], b13[:, I + rank * ip:I + (rank + 1) * ip])
-        assert torch.equal(layer.w2_bias.data, b2 if rank == 0 else torch.zeros_like(b2))  # rank 0 only
+
+        # gpt-oss checkpoints: all-expert tensors, gate/up rows interleaved and fused ("w13"), biases beside them
+        # (utils/loader.py:41-49; layers/fused_moe.py:388-392,647-654): a rank takes a contiguous slice of the
+        # fused rows and of the fused bias, w2_bias lives on rank 0 only
+        goss = FusedMoE(E, k, H, I, params_dtype=torch.bfloat16, activation="swigluoai", has_bias=True)
+        goss.weight_loader(goss.w13_weight, w13.clone(), "model.layers.0.mlp.experts.gate_up_proj_blocks", "w13", 0)
+        goss.weight_loader(goss.w2_weight, w2.clone(), "model.layers.0.mlp.experts.down_proj_blocks", "w2", 0)
+        goss.weight_loader(goss.w13_bias, b13.clone(), "model.layers.0.mlp.experts.gate_up_proj_bias", "w13", 0)
+        goss.weight_loader(goss.w2_bias, b2.clone(), "model.layers.0.mlp.experts.down_proj_bias", "w2", 0)
+        g13, g2 = O.shard_expert_weights(w13, w2, world, rank, "swigluoai")
+        assert torch.equal(goss.w13_weight.data, g13) and torch.equal(goss.w2_weight.data, g2)
+        assert torch.equal(goss.w13_bias.data, b13[:, 2 * rank * ip:2 * (rank + 1) * ip])
+        assert torch.equal(goss.w2_bias.data, b2 if rank == 0 else torch.zeros_like(b2))  # rank 0 only
+        whole = FusedMoE(E, k, H, I, params_dtype=torch.bfloat16, has_bias=True)
+        whole.weight_loader(whole.w13_bias, goss.w13_bias.data.clone(), "experts.gate_up_proj_bias", "all", 0)
+        assert torch.equal(whole.w13_bias.data, goss.w13_bias.data)
+        try:
+            layer.weight_loader(layer.w2_weight, w2[0], "model.layers.0.mlp.experts.0.down_proj", "w2", 0)
+            raise AssertionError("a name without weight / block / bias must be refused, as the reference refuses it")
+        except ValueError:
+            pass
 
         # partial block on this rank's shard (CPU oracle), reduced over the ranks == the full block
         tw, ti, _ = O.fused_topk(x, logits, k, True)
-        part = O.fused_experts(x, layer.w13_weight.data, layer.w2_weight.data, tw, ti, mode="exact",
-                               w13_bias=layer.w13_bias.data, w2_bias=layer.w2_bias.data).float()
+        part = O.fused_experts(x, goss.w13_weight.data, goss.w2_weight.data, tw, ti, "swigluoai", mode="exact",
+                               w13_bias=goss.w13_bias.data, w2_bias=goss.w2_bias.data).float()
         dist.all_reduce(part)
-        full = O.fused_experts(x, w13, w2, tw, ti, mode="exact", w13_bias=b13, w2_bias=b2).float()
+        full = O.fused_experts(x, w13, w2, tw, ti, "swigluoai", mode="exact", w13_bias=b13, w2_bias=b2).float()
         assert O.rel_l2(part, full) < 8e-3
 
         # fp8 shards: sliced like the bf16 weights, scales of the unsharded tensors; I / world = 192 puts rank 1's
