@@ -244,6 +244,17 @@ class Ctx:
             dist.barrier()
             torch.cuda.synchronize()
 
+    def check_status(self, where: str):
+        """Device status word of every rank (non-zero: a bounded device-side wait ran out). All ranks learn the
+        worst value and leave together, so nobody is left waiting in a collective for a rank that quit."""
+        from layered_prefill_b200 import ops
+        status = ops.read_status(self.dev)
+        worst = int(self.max_over_ranks(float(status)))
+        if worst != 0:
+            if self.rank == 0:
+                print(json.dumps({"error": f"device-side wait timed out {where}", "status": worst}), file=sys.stderr, flush=True)
+            raise SystemExit(4)
+
     def max_over_ranks(self, v: float) -> float:
         if self.world == 1:
             return v
@@ -370,9 +381,13 @@ def run_workload(ctx: Ctx, wl, steps: int, warmup: int, primary: bool, mixed: bo
 
     sampler = ClockSampler(dev.index or 0)
     sampler.start()
+    # the ranks start together: the peer-memory reduction waits for a peer for a bounded time only, and rank 0
+    # has just spent longer than that copying a weight set to the host
+    ctx.barrier()
     for i in range(warmup):
         step(i)
     ctx.barrier()
+    ctx.check_status("during warm-up")
 
     # ---- parity of the first step's output (outside every timed region): the ranks hold identical bits, and rank 0
     # checks them against the CPU oracle on the same inputs (all tokens up to 256, a spread sample of 96 beyond)
@@ -436,8 +451,7 @@ def run_workload(ctx: Ctx, wl, steps: int, warmup: int, primary: bool, mixed: bo
         for i in range(max(3, n_sets)):
             step(i)
         ctx.barrier()
-    if ops.read_status(dev) != 0:
-        raise SystemExit("device-side wait timed out during warm-up")
+    ctx.check_status("during graph warm-up")
 
     # ---- timed region: exactly `steps` steps between CUDA events on the launching stream, barrier and
     # synchronize on both sides, max over ranks; repeated for `rounds` rounds, the median round is reported
@@ -467,9 +481,7 @@ def run_workload(ctx: Ctx, wl, steps: int, warmup: int, primary: bool, mixed: bo
     ms_total = srt[len(srt) // 2]
     ms_per_step = ms_total / steps
     clocks = sampler.summary(t_wall0, t_wall1)
-    status = ops.read_status(dev)
-    if status != 0:
-        raise SystemExit(f"device-side wait timed out (status {status})")
+    ctx.check_status("in the timed region")
     timed_rounds = {"rounds": rounds, "steps_per_round": steps, "median_ms": ms_total, "min_ms": srt[0], "max_ms": srt[-1],
                     "reported": "median round"}
 
@@ -918,9 +930,11 @@ def main():
         saved_stdout = os.dup(1)
         os.dup2(2, 1)
         try:
-            dist.init_process_group("nccl", device_id=dev)
+            # short collective timeouts: a rank that dropped out ends the run in minutes, not in half an hour
+            from datetime import timedelta
+            dist.init_process_group("nccl", device_id=dev, timeout=timedelta(seconds=180))
             from layered_prefill_b200.custom_all_reduce import CustomAllreduce
-            comm = CustomAllreduce(group=dist.new_group(backend="gloo"), device=dev)
+            comm = CustomAllreduce(group=dist.new_group(backend="gloo", timeout=timedelta(seconds=180)), device=dev)
             dist.barrier()
             torch.cuda.synchronize()
         finally:
@@ -929,6 +943,8 @@ def main():
             os.close(saved_stdout)
         if comm.disabled:
             raise SystemExit("peer-memory all-reduce could not be initialised on this box")
+        from layered_prefill_b200._lib import check as _check, lib as _lib
+        _check(_lib.moe_b200_ar_set_wait_limit_ns(comm._ptr, 20_000_000_000))  # ranks of a benchmark may drift by seconds
     ctx = Ctx(args, world, rank, dev, comm)
 
     prefill = wl.T >= 2048
