@@ -259,6 +259,12 @@ int moe_b200_ar_register_buffer(int64_t handle, const int64_t* ptrs);
  * barrier (the next call's opening barrier proves that every peer has finished the previous one). Optional; without
  * it the fused call keeps both barriers. No reference counterpart. bytes: size of the buffer, a multiple of 32. */
 int moe_b200_ar_register_fused_buffer(int64_t handle, const int64_t* ptrs, int64_t bytes);
+/* Receive areas (one per rank, zero-initialised, used by nothing else) of the flag-in-data one-shot reduction that
+ * moe_b200_ar_moe_sum_all_reduce takes for tensors of up to bytes / (4 * world) bytes: every 16-byte vector travels
+ * as two packets {data, flag, data, flag} stored straight into the peers' areas, and a receiver polls its own
+ * memory, so the call needs no barrier at all. No counterpart in the reference (its kernels all use the two
+ * flag barriers of csrc/custom_all_reduce.cuh:199-241). Pass algo = 3 to a reduction to keep it off this path. */
+int moe_b200_ar_register_ll_buffer(int64_t handle, const int64_t* ptrs, int64_t bytes);
 /* out = sum over ranks of inp (bf16/fp16/fp32 by element_size+is_bf16), fp32 accumulation in rank
  * order, identical bits on every rank. If reg_buffer != 0 the input is first copied there
  * (ops.all_reduce, custom_all_reduce_kernels.cu:64-107). algo: 0 auto, 1 one-shot, 2 two-shot. */

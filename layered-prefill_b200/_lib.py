@@ -82,6 +82,7 @@ SIGNATURES = {
     "moe_b200_ar_dispose": (c_int, [c_int64]),
     "moe_b200_ar_register_buffer": (c_int, [c_int64, POINTER(c_int64)]),
     "moe_b200_ar_register_fused_buffer": (c_int, [c_int64, POINTER(c_int64), c_int64]),
+    "moe_b200_ar_register_ll_buffer": (c_int, [c_int64, POINTER(c_int64), c_int64]),
     "moe_b200_ar_all_reduce": (c_int, [c_int64, c_void_p, c_void_p, c_int64, c_int, c_int64, c_int64, c_int, c_void_p, c_void_p]),
     "moe_b200_ar_moe_sum_all_reduce": (c_int, [c_int64, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int, c_void_p, c_void_p]),
     "moe_b200_ar_all_reduce_add_rms_norm": (c_int, [c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_int64, c_int64, c_int, c_void_p, c_void_p]),

@@ -8,7 +8,7 @@
 // is the r-th in ascending order, where the reference's atomicAdd scatter leaves the order
 // to arrival time), and for large inputs the histogram and the scatter run on many CTAs
 // (one per 1024 flat indices) around a one-CTA scan, instead of one CTA for everything.
-// Three size classes: up to 1024 flat indices (decode) one CTA with a rank-by-counting placement,
+// Three size classes: up to 1024 flat indices and 256 experts (decode) one CTA that ranks by warp match,
 // up to 4096 one CTA with warp-ordered placement, above that the three multi-CTA kernels.
 #include "launch.cuh"
 #include "moe_b200_internal.cuh"
@@ -127,49 +127,55 @@ align_single_cta_kernel(const int* __restrict__ topk_ids, int numel, int E, int 
   for (int base = 0; base < numel; base += kThreads) stable_place_chunk(topk_ids, base, numel, E, counts, sorted_ids);
 }
 
-// Decode-sized inputs (up to 1024 flat indices, one per thread): no turn-taking at all. The expert of every
-// index sits in shared memory, and an index finds its place inside its expert by counting the equal entries
-// in front of it (16-byte broadcast reads, at most 256 of them), which is the stable ascending order again.
+// Decode-sized inputs (up to 1024 flat indices, one per thread; up to 256 experts): no turn-taking at all. A warp
+// ranks its 32 indices among themselves with one match instruction, per-warp counts go to a [warp][expert] table,
+// one thread per expert turns its column into a prefix over the warps, and an index lands at
+// cumsum[expert] + (indices of that expert in earlier warps) + (rank inside its warp): ascending order again.
+constexpr int kTinyExperts = 256;
+
 __global__ void __launch_bounds__(kThreads)
 align_tiny_kernel(const int* __restrict__ topk_ids, int numel, int E, int block_size, int* __restrict__ sorted_ids,
                   int sorted_cap, int* __restrict__ expert_ids, int expert_ids_cap, int* __restrict__ num_post_pad) {
-  __shared__ __align__(16) int ids_s[kThreads];
-  __shared__ int counts[kMaxExperts];
+  __shared__ int warp_cnt[32 * kTinyExperts];  // [warp][expert]
+  __shared__ int counts[kTinyExperts];
   __shared__ int warp_totals[32];
   __shared__ int total_smem;
   grid_dependency_launch();
   grid_dependency_wait();
 
   const int i = threadIdx.x;
+  const int lane = i & 31;
+  const int warp = i >> 5;
+  const int live_warps = (numel + 31) / 32;
   for (int s = threadIdx.x; s < sorted_cap; s += kThreads) sorted_ids[s] = numel;
-  for (int e = threadIdx.x; e < E; e += kThreads) counts[e] = 0;
+  for (int c = threadIdx.x; c < live_warps * E; c += kThreads) warp_cnt[(c / E) * kTinyExperts + c % E] = 0;
   int e = -1;
   if (i < numel) {
     const int id = topk_ids[i];
     if (id >= 0 && id < E) e = id;
   }
-  ids_s[i] = e;
   __syncthreads();
-  if (e >= 0) atomicAdd(&counts[e], 1);
+  int rank = 0;
+  if (warp < live_warps) {
+    const int key = e >= 0 ? e : -1 - lane;  // lanes without a valid expert match nobody
+    const unsigned peers = __match_any_sync(0xffffffffu, key);
+    rank = __popc(peers & ((1u << lane) - 1u));
+    if (e >= 0 && rank == 0) warp_cnt[warp * kTinyExperts + e] = __popc(peers);
+  }
   __syncthreads();
-  const int my_count = threadIdx.x < E ? counts[threadIdx.x] : 0;
+  int my_count = 0;
+  if (threadIdx.x < E) {
+    for (int w = 0; w < live_warps; ++w) {
+      const int c = warp_cnt[w * kTinyExperts + threadIdx.x];
+      warp_cnt[w * kTinyExperts + threadIdx.x] = my_count;
+      my_count += c;
+    }
+  }
   const int start = scan_and_publish(my_count, E, block_size, sorted_cap, expert_ids_cap, expert_ids, num_post_pad,
                                      warp_totals, &total_smem);
-  __syncthreads();
-  if (threadIdx.x < E) counts[threadIdx.x] = start;  // counts[] now = first slot of each expert
-  __syncthreads();
-  const int warp_base = i & ~31;
-  if (warp_base < numel) {
-    int rank = 0;
-    const int4* v = reinterpret_cast<const int4*>(ids_s);
-    const int key = e >= 0 ? e : -2;  // an index without a valid expert matches nothing
-    for (int j4 = 0; j4 * 4 < warp_base + 32; ++j4) {
-      const int4 q = v[j4];
-      const int j = j4 * 4;
-      rank += (q.x == key && j < i) + (q.y == key && j + 1 < i) + (q.z == key && j + 2 < i) + (q.w == key && j + 3 < i);
-    }
-    if (e >= 0) sorted_ids[counts[e] + rank] = i;
-  }
+  if (threadIdx.x < E) counts[threadIdx.x] = start;
+  __syncthreads();  // also orders the fill of sorted_ids above before the placements below
+  if (e >= 0) sorted_ids[counts[e] + warp_cnt[warp * kTinyExperts + e] + rank] = i;
 }
 
 // ---- large inputs: histogram per 1024-index chunk / one-CTA scan / stable scatter per chunk
@@ -246,7 +252,7 @@ int launch_align_block_size(const int* topk_ids, int numel, int E, int block_siz
                             size_t workspace_bytes, cudaStream_t stream) {
   if (E <= 0 || E > kMaxExperts) return set_error(kStatusInvalidArgument, "moe_align_block_size: 1..1024 experts");
   if (block_size <= 0 || numel < 0) return set_error(kStatusInvalidArgument, "moe_align_block_size: bad sizes");
-  if (numel <= kThreads) {
+  if (numel <= kThreads && E <= kTinyExperts) {
     launch_pdl(align_tiny_kernel, dim3(1), dim3(kThreads), 0, stream, topk_ids, numel, E, block_size, sorted_ids,
                sorted_cap, expert_ids, expert_ids_cap, num_post_pad);
     count_launches(1);

@@ -38,7 +38,7 @@ namespace moe_b200 {
 namespace {
 
 constexpr int kMaxRanks = 8;
-constexpr int kMaxArBlocks = 128;
+constexpr int kMaxArBlocks = 160;  // up to one block per SM (148 on B200) for large messages
 constexpr int kArThreads = 512;
 constexpr int kFusedBlocks = 32;  // fixed grid of the barrier-saving one-shot kernel (its per-block call counters rely on it)
 
@@ -46,6 +46,7 @@ struct alignas(128) Signal {
   uint32_t arrive[kMaxArBlocks][kMaxRanks];  // arrive[b][r]: written by block b of rank r
   uint32_t epoch[kMaxArBlocks];              // this rank's barrier count per block
   uint32_t fused_calls[kFusedBlocks];        // this rank's count of barrier-saving one-shot calls, per block
+  uint32_t ll_calls[kFusedBlocks];           // this rank's count of flag-in-data one-shot calls, per block
 };
 constexpr size_t kMetaBytes = (sizeof(Signal) + 255) / 256 * 256;
 
@@ -167,6 +168,41 @@ __device__ __forceinline__ uint4 reduce_ranks(const uint4* const* ptrs, long lon
   return o.u;
 }
 
+// How many vectors a thread keeps in flight per rank: about sixteen 16-byte peer loads per thread before the
+// first add, which is what it takes to cover the NVLink round trip at two and four ranks.
+template <int N> struct Unroll { static constexpr int kU = N <= 2 ? 8 : N <= 4 ? 4 : 2; };
+
+// dst[j] = sum over ranks of ptrs[r][base + j] for j in [0, count), fp32 in rank order, this thread's share.
+template <typename T, int N>
+__device__ __forceinline__ void reduce_span(const uint4* const* ptrs, long long base, long long count, uint4* dst,
+                                            long long tid, long long stride) {
+  constexpr int U = Unroll<N>::kU;
+  for (long long j = tid; j < count; j += stride * U) {
+    Vec16 v[U][N];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long jj = j + u * stride;
+      if (jj < count) {
+#pragma unroll
+        for (int r = 0; r < N; ++r) v[u][r].u = ld_cg(ptrs[r] + base + jj);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long jj = j + u * stride;
+      if (jj < count) {
+        float acc[VecTraits<T>::kElems];
+        VecTraits<T>::set(acc, v[u][0]);
+#pragma unroll
+        for (int r = 1; r < N; ++r) VecTraits<T>::add(acc, v[u][r]);
+        Vec16 o;
+        VecTraits<T>::pack(o, acc);
+        dst[jj] = o.u;
+      }
+    }
+  }
+}
+
 // partial[t, 8 cols] = bf16(sum over k slots), written to this rank's registered buffer
 __device__ __forceinline__ void slot_sum_vec(const ArParams& p, uint4* own, long long v) {
   const long long t = v / p.hidden_vecs;
@@ -200,8 +236,7 @@ __global__ void __launch_bounds__(kArThreads, 1) ar_oneshot_kernel(const ArParam
     for (long long v = tid; v < p.nvec; v += stride) slot_sum_vec(p, own, v);
   }
   peer_barrier<N>(p, true, &timed_out);
-  uint4* out = static_cast<uint4*>(p.out);
-  for (long long v = tid; v < p.nvec; v += stride) out[v] = reduce_ranks<T, N>(ptrs, v);
+  reduce_span<T, N>(ptrs, 0, p.nvec, static_cast<uint4*>(p.out), tid, stride);
   // nobody may overwrite its input while a peer still reads it
   peer_barrier<N>(p, false, &timed_out);
 }
@@ -234,6 +269,107 @@ __global__ void __launch_bounds__(kArThreads, 1) ar_oneshot_sum_kernel(const ArP
   uint4* out = static_cast<uint4*>(p.out);
   for (long long v = tid; v < p.nvec; v += stride) out[v] = reduce_ranks<__nv_bfloat16, N>(ptrs, v);
   if (threadIdx.x == 0) p.self_sg->fused_calls[blockIdx.x] = call + 1u;
+}
+
+// k-slot sum + one-shot all-reduce with NO barrier: every 16-byte vector of this rank's partial sum travels as two
+// 16-byte packets {data, flag, data, flag} whose flag words carry the call number, pushed with plain stores into a
+// receive area of every rank (its own included); a receiver polls ITS OWN memory until both packets of a vector
+// show the current call number, so the data needs no fence, no flag round trip and no remote load: one NVLink
+// crossing per rank pair instead of three. (Eight-byte stores arrive whole over NVLink, which is what NCCL's
+// low-latency protocol relies on as well; twice the bytes on the wire, which is why this path is for
+// decode-sized tensors only.) Receive areas alternate with the parity of the call number, and a rank cannot be
+// two calls ahead of a peer (to finish call n + 1 it needs that peer's packets of call n + 1, sent by a kernel that
+// started after the peer's call n had finished), so nobody overwrites packets that are still being read. The sum
+// is fp32 in rank order, one rounding: the bits of the barrier kernels.
+struct LLParams {
+  RankData* areas;        // device tuple: the receive area of every rank
+  long long slot_vecs;    // vectors per (parity, source rank) slot of a receive area
+};
+
+__device__ __forceinline__ void st_ll(uint4* dst, uint32_t a, uint32_t b, uint32_t flag) {
+  asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "r"(a), "r"(flag), "r"(b), "r"(flag) : "memory");
+}
+__device__ __forceinline__ uint4 ld_ll(const uint4* src) {
+  uint4 v;
+  asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(src) : "memory");
+  return v;
+}
+
+template <int N>
+__global__ void __launch_bounds__(kArThreads, 1) ar_ll_sum_kernel(const ArParams p, const LLParams ll) {
+  grid_dependency_launch();
+  grid_dependency_wait();
+  const uint32_t epoch = p.self_sg->ll_calls[blockIdx.x] + 1u;
+  const long long parity_off = (epoch & 1u) ? static_cast<long long>(N) * ll.slot_vecs : 0;
+  const RankData areas = *ll.areas;
+  uint4* area[N];
+#pragma unroll
+  for (int r = 0; r < N; ++r) area[r] = static_cast<uint4*>(const_cast<void*>(areas.ptrs[r]));
+  const long long tid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  // push: this rank's slot in everybody's receive area, two packets per vector
+  for (long long v = tid; v < p.nvec; v += stride) {
+    const long long t = v / p.hidden_vecs;
+    const int c = static_cast<int>(v % p.hidden_vecs);
+    const uint4* src = reinterpret_cast<const uint4*>(p.c3) + (t * p.top_k) * p.hidden_vecs + c;
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int j = 0; j < p.top_k; ++j) {
+      Vec16 x;
+      x.u = src[static_cast<long long>(j) * p.hidden_vecs];
+      VecTraits<__nv_bfloat16>::add(acc, x);
+    }
+    Vec16 o;
+    VecTraits<__nv_bfloat16>::pack(o, acc);
+    const long long slot = (parity_off + static_cast<long long>(p.rank) * ll.slot_vecs + v) * 2;
+#pragma unroll
+    for (int r = 0; r < N; ++r) {
+      st_ll(area[r] + slot, o.u.x, o.u.y, epoch);
+      st_ll(area[r] + slot + 1, o.u.z, o.u.w, epoch);
+    }
+  }
+  // receive: poll this rank's own area until every rank's packets of this call are there
+  const uint4* mine = area[0];
+#pragma unroll
+  for (int r = 1; r < N; ++r)
+    if (r == p.rank) mine = area[r];
+  uint4* out = static_cast<uint4*>(p.out);
+  bool ok = true;
+  for (long long v = tid; v < p.nvec && ok; v += stride) {
+    uint4 lo[N], hi[N];
+    const unsigned long long t0 = globaltimer_ns();
+    uint32_t spins = 0;
+    while (true) {
+      bool all = true;
+#pragma unroll
+      for (int r = 0; r < N; ++r) {
+        const long long slot = (parity_off + static_cast<long long>(r) * ll.slot_vecs + v) * 2;
+        lo[r] = ld_ll(mine + slot);
+        hi[r] = ld_ll(mine + slot + 1);
+        all = all && lo[r].y == epoch && lo[r].w == epoch && hi[r].y == epoch && hi[r].w == epoch;
+      }
+      if (all) break;
+      if ((++spins & 63u) == 0u && globaltimer_ns() - t0 > p.wait_limit_ns) {
+        atomicCAS(p.status, 0, kErrPeerWait);
+        ok = false;
+        break;
+      }
+    }
+    if (!ok) break;
+    float acc[8];
+    Vec16 x;
+    x.u = make_uint4(lo[0].x, lo[0].z, hi[0].x, hi[0].z);
+    VecTraits<__nv_bfloat16>::set(acc, x);
+#pragma unroll
+    for (int r = 1; r < N; ++r) {
+      x.u = make_uint4(lo[r].x, lo[r].z, hi[r].x, hi[r].z);
+      VecTraits<__nv_bfloat16>::add(acc, x);
+    }
+    Vec16 o;
+    VecTraits<__nv_bfloat16>::pack(o, acc);
+    out[v] = o.u;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) p.self_sg->ll_calls[blockIdx.x] = epoch;
 }
 
 // One-shot all-reduce that ends in the next layer's residual add + RMSNorm (what the decoder layer after the MoE
@@ -317,15 +453,26 @@ __global__ void __launch_bounds__(kArThreads, 1) ar_twoshot_kernel(const ArParam
   }
   peer_barrier<N>(p, true, &timed_out);
   // reduce-scatter: this rank's slice from every peer into its own scratch
-  uint4* my_tmp = tmps[p.rank];
-  for (long long j = tid; j < my_len; j += stride) my_tmp[j] = reduce_ranks<T, N>(ptrs, my_start + j);
+  reduce_span<T, N>(ptrs, my_start, my_len, tmps[p.rank], tid, stride);
   peer_barrier<N>(p, true, &timed_out);
-  // all-gather
+  // all-gather: the loads of several slices' vectors go out before the first store
   uint4* out = static_cast<uint4*>(p.out);
-  for (long long j = tid; j < largest; j += stride) {
+  constexpr int U = Unroll<N>::kU;
+  for (long long j = tid; j < largest; j += stride * U) {
+    uint4 g[U][N];
 #pragma unroll
-    for (int r = 0; r < N; ++r) {
-      if (r == N - 1 || j < part) out[r * part + j] = ld_cg(tmps[r] + j);
+    for (int u = 0; u < U; ++u) {
+      const long long jj = j + u * stride;
+#pragma unroll
+      for (int r = 0; r < N; ++r)
+        if (jj < largest && (r == N - 1 || jj < part)) g[u][r] = ld_cg(tmps[r] + jj);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long jj = j + u * stride;
+#pragma unroll
+      for (int r = 0; r < N; ++r)
+        if (jj < largest && (r == N - 1 || jj < part)) out[r * part + jj] = g[u][r];
     }
   }
 }
@@ -359,6 +506,8 @@ struct Comm {
   int env_algo = 0;               // 1 = one-shot, 2 = two-shot forced by VLLM_CUSTOM_ALLREDUCE_ALGO at init time
   RankData* fused_rd = nullptr;   // the double buffer of the barrier-saving one-shot kernel (registered, used by nothing else)
   long long fused_bytes = 0;
+  RankData* ll_rd = nullptr;      // receive areas of the flag-in-data one-shot kernel
+  long long ll_bytes = 0;
 };
 
 typedef CUresult (*PointerGetAttributeFn)(void*, CUpointer_attribute, CUdeviceptr);
@@ -387,7 +536,7 @@ int pick_blocks(long long nvec) {
 
 bool use_oneshot(const Comm& c, long long bytes, int algo) {
   if (algo == 0) algo = c.env_algo;  // a call's own choice wins over the environment's
-  if (algo == 1) return true;
+  if (algo == 1 || algo == 3) return true;  // 3: one-shot with barriers (never the flag-in-data kernel)
   if (algo == 2) return false;
   if (c.world == 2) return true;
   if (c.world <= 4) return bytes <= 512 * 1024;
@@ -456,6 +605,24 @@ int ar_moe_sum_all_reduce_impl(int64_t handle, const void* c3, void* out, int T,
   p.nvec = bytes / 16; p.wait_limit_ns = c->wait_limit_ns; p.status = status_word;
   p.c3 = static_cast<const __nv_bfloat16*>(c3); p.top_k = k; p.hidden_vecs = H / 8;
   const bool oneshot = use_oneshot(*c, bytes, algo);
+  // flag-in-data path: a receive area holds 2 parities x world slots of 32-byte packet pairs
+  const long long ll_slot_vecs = c->ll_rd != nullptr ? c->ll_bytes / (2ll * c->world * 32) : 0;
+  if (oneshot && algo != 3 && ll_slot_vecs >= bytes / 16) {
+    LLParams ll{c->ll_rd, ll_slot_vecs};
+#define MOE_B200_ARL_CASE(n) \
+  case n: launch_pdl(ar_ll_sum_kernel<n>, dim3(kFusedBlocks), dim3(kArThreads), 0, stream, p, ll); break;
+    switch (c->world) {
+      MOE_B200_ARL_CASE(2)
+      MOE_B200_ARL_CASE(4)
+      MOE_B200_ARL_CASE(6)
+      MOE_B200_ARL_CASE(8)
+      default:
+        return set_error(kStatusInvalidArgument, "custom allreduce only supports num gpus in (2,4,6,8). Actual num gpus = %d", c->world);
+    }
+#undef MOE_B200_ARL_CASE
+    count_launches(1);
+    return check_launch("moe_sum_all_reduce (flag-in-data)");
+  }
   if (oneshot && c->fused_rd != nullptr && bytes <= c->fused_bytes / 2) {
     p.rank_data = c->fused_rd;
     const long long half_vecs = c->fused_bytes / 2 / 16;
@@ -619,6 +786,16 @@ int moe_b200_ar_register_fused_buffer(int64_t handle, const int64_t* ptrs, int64
   if (int st = moe_b200_ar_register_buffer(handle, ptrs)) return st;
   c->fused_rd = c->buffers[reinterpret_cast<const void*>(static_cast<intptr_t>(ptrs[c->rank]))];
   c->fused_bytes = bytes;
+  return kStatusOk;
+}
+
+int moe_b200_ar_register_ll_buffer(int64_t handle, const int64_t* ptrs, int64_t bytes) {
+  Comm* c = as_comm(handle);
+  if (c == nullptr || ptrs == nullptr || bytes < 64 * c->world || bytes % 64 != 0)
+    return set_error(kStatusInvalidArgument, "register_ll_buffer: null argument or a size that is not a multiple of 64");
+  if (int st = moe_b200_ar_register_buffer(handle, ptrs)) return st;
+  c->ll_rd = c->buffers[reinterpret_cast<const void*>(static_cast<intptr_t>(ptrs[c->rank]))];
+  c->ll_bytes = bytes;
   return kStatusOk;
 }
 

@@ -25,6 +25,7 @@ from ._lib import check, lib
 MiB = 1024 * 1024
 DEFAULT_MAX_SIZE = 64 * MiB
 FUSED_BUFFER_BYTES = 1 * MiB  # two halves of 512 KiB = the largest one-shot message at 4 ranks
+LL_MAX_MESSAGE_BYTES = 256 * 1024  # decode batches: 64 tokens x 2048 hidden bf16; the receive area is 4 x world x this
 
 
 def is_weak_contiguous(inp: torch.Tensor) -> bool:
@@ -106,6 +107,10 @@ class CustomAllreduce:
             # so needs no closing barrier); nothing else may write this buffer
             self.fused_ptrs = self.create_shared_buffer(FUSED_BUFFER_BYTES, group=self.gloo_group)
             ops.register_fused_buffer(self._ptr, self.fused_ptrs, FUSED_BUFFER_BYTES)
+            # receive areas of the flag-in-data reduction: 2 parities x world source slots x 2 x message bytes
+            self.ll_bytes = 4 * world_size * LL_MAX_MESSAGE_BYTES
+            self.ll_ptrs = self.create_shared_buffer(self.ll_bytes, group=self.gloo_group)
+            ops.register_ll_buffer(self._ptr, self.ll_ptrs, self.ll_bytes)
 
     @contextmanager
     def capture(self):
@@ -174,6 +179,23 @@ class CustomAllreduce:
                 ops.status_word(inp.device).data_ptr(), torch.cuda.current_stream().cuda_stream))
         return normed, residual
 
+    def staging_view(self, shape, dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+        """A tensor over the start of this rank's peer-visible staging buffer (no copy, no allocation): a producer
+        that writes its result here (e.g. a GEMM with out=) feeds all_reduce / all_reduce_add_rms_norm without the
+        staging copy. The buffer is shared by every staged call of this communicator: use the view at once."""
+        numel = 1
+        for d in shape:
+            numel *= int(d)
+        nbytes = numel * torch.empty((), dtype=dtype).element_size()
+        if self.disabled or nbytes > self.max_size:
+            raise ValueError(f"staging_view: {nbytes} bytes do not fit the registered buffer")
+
+        class _Raw:  # CUDA array interface v2 over the raw device pointer (bytes; viewed as `dtype` below)
+            __cuda_array_interface__ = {"shape": (max(nbytes, 1),), "typestr": "|u1",
+                                        "data": (int(self.buffer_ptrs[self.rank]), False), "version": 2}
+        raw = torch.as_tensor(_Raw(), device=self.device)
+        return raw[:nbytes].view(dtype).view(*shape)
+
     def custom_all_reduce(self, input: torch.Tensor) -> Optional[torch.Tensor]:  # noqa: A002
         """custom_all_reduce.py:276-292."""
         if self.disabled or not self.should_custom_ar(input):
@@ -192,7 +214,7 @@ class CustomAllreduce:
             ops.dispose(self._ptr)
             self._ptr = 0
             self.disabled = True
-            for ptrs in (self.meta_ptrs, self.buffer_ptrs, self.fused_ptrs):
+            for ptrs in (self.meta_ptrs, self.buffer_ptrs, self.fused_ptrs, self.ll_ptrs):
                 for i, p in enumerate(ptrs):
                     if i != self.rank and p:
                         ops.close_mem_handle(p)
@@ -203,6 +225,7 @@ class CustomAllreduce:
             self.free_shared_buffer(self.meta_ptrs, rank=self.rank)
             self.free_shared_buffer(self.buffer_ptrs, rank=self.rank)
             self.free_shared_buffer(self.fused_ptrs, rank=self.rank)
+            self.free_shared_buffer(self.ll_ptrs, rank=self.rank)
 
     def __del__(self):
         try:

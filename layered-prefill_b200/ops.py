@@ -215,6 +215,13 @@ def register_fused_buffer(fa: int, ipc_ptrs: List[int], nbytes: int) -> None:
     check(lib.moe_b200_ar_register_fused_buffer(fa, arr, nbytes))
 
 
+def register_ll_buffer(fa: int, ipc_ptrs: List[int], nbytes: int) -> None:
+    """The receive areas of the flag-in-data one-shot reduction (data and flag travel in the same 8 bytes, no
+    barrier). No reference counterpart."""
+    arr = (ctypes.c_int64 * len(ipc_ptrs))(*ipc_ptrs)
+    check(lib.moe_b200_ar_register_ll_buffer(fa, arr, nbytes))
+
+
 _AR_DTYPES = {torch.bfloat16: 0, torch.float16: 1, torch.float32: 2}
 
 

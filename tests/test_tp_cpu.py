@@ -139,6 +139,7 @@ def _worker(rank, world, port, q):
         c2.meta_ptrs = [10 + r for r in range(world)]
         c2.buffer_ptrs = [20 + r for r in range(world)]
         c2.fused_ptrs = [30 + r for r in range(world)]
+        c2.ll_ptrs = [40 + r for r in range(world)]
         car.ops = FakeLifecycleOps
         try:
             c2.close()
@@ -148,8 +149,8 @@ def _worker(rank, world, port, q):
         assert calls[0] == ("dispose", 77) and c2.disabled and c2._ptr == 0
         closes = [c for c in calls if c[0] == "close"]
         frees = [c for c in calls if c[0] == "free"]
-        assert sorted(p for _, p in closes) == sorted(b + r for b in (10, 20, 30) for r in range(world) if r != rank)
-        assert [p for _, p in frees] == [10 + rank, 20 + rank, 30 + rank]
+        assert sorted(p for _, p in closes) == sorted(b + r for b in (10, 20, 30, 40) for r in range(world) if r != rank)
+        assert [p for _, p in frees] == [10 + rank, 20 + rank, 30 + rank, 40 + rank]
         assert max(calls.index(c) for c in closes) < min(calls.index(f) for f in frees)
         assert not car.is_weak_contiguous(torch.zeros(4, 4)[:, :2]) and car.is_weak_contiguous(torch.zeros(4, 4)[2:])
         dist.barrier()

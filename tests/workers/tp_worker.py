@@ -4,7 +4,8 @@ Checks, on every rank, against the CPU oracle:
   1. plain peer-memory all-reduce (one-shot and two-shot, staged and registered input) on several sizes;
   2. the fused k-slot-sum + all-reduce;
   3. the whole tensor-parallel MoE block (I sharded as the reference's weight_loader does);
-  4. a graph-captured all-reduce; 5. the all-reduce that ends in the next layer's add + RMSNorm.
+  4. a graph-captured all-reduce; 5. the all-reduce that ends in the next layer's add + RMSNorm, also behind
+     the row-parallel linear (o_proj).
 Prints "TP_WORKER_OK rank=<r>" on success; any failure raises.
 """
 import os
@@ -54,7 +55,10 @@ def main():
 
     # ---- 2. fused k-slot sum + all-reduce (both algorithms)
     from layered_prefill_b200._lib import check, lib
-    for T, k, H, algo in ((64, 8, 2048, 1), (64, 8, 2048, 2), (300, 4, 512, 2), (1, 2, 64, 1)):
+    # algo 0 / 1: decode-sized tensors take the flag-in-data kernel (no barrier); 3: one-shot with barriers
+    # (the one-barrier kernel on its alternating halves); 2: two-shot
+    for T, k, H, algo in ((64, 8, 2048, 1), (64, 8, 2048, 2), (64, 8, 2048, 3), (300, 4, 512, 2), (1, 2, 64, 1),
+                          (1, 2, 64, 3), (17, 8, 2048, 0), (64, 8, 2048, 0)):
         c3s = []
         for r in range(world):
             g = torch.Generator().manual_seed(T * 7 + r)
@@ -233,6 +237,37 @@ def main():
     assert torch.equal(res_a, res_b) and torch.equal(norm_a, norm_b)
     assert ops.read_status(dev) == 0
 
+    # ---- 5b. the row-parallel linear (o_proj, nanovllm/layers/linear.py:155-201) through the same tail: product
+    # written into the peer-visible buffer, reduction + residual add + norm in one call; same bits as
+    # forward() followed by add_rms_norm, and close to the unsharded fp32 product
+    from layered_prefill_b200.linear import RowParallelLinear
+    for T, K, Nout, use_bias in ((64, 4096, 2048, False), (5, 512, 256, True), (700, 1024, 2048, False)):
+        g = torch.Generator().manual_seed(T + K)
+        w_full = (torch.randn(Nout, K, generator=g) * 0.03).to(torch.bfloat16)
+        b_full = torch.randn(Nout, generator=g).to(torch.bfloat16)
+        x_full = torch.randn(T, K, generator=g).to(torch.bfloat16)
+        res0 = torch.randn(T, Nout, generator=g).to(torch.bfloat16)
+        wn = (1 + 0.1 * torch.randn(Nout, generator=g)).to(torch.bfloat16).to(dev)
+        lin = RowParallelLinear(K, Nout, bias=use_bias).to(dev).to(torch.bfloat16)
+        assert lin.weight.shape == (Nout, K // world) and lin.tp_size == world
+        lin.weight_loader(lin.weight, w_full.to(dev))
+        if use_bias:
+            lin.bias.data.zero_()
+            lin.weight_loader(lin.bias, b_full.to(dev))
+        kp = K // world
+        x_shard = x_full[:, rank * kp:(rank + 1) * kp].contiguous().to(dev)
+        y = lin(x_shard)
+        res_a, norm_a = res0.to(dev).clone(), torch.empty(T, Nout, dtype=torch.bfloat16, device=dev)
+        ops.add_rms_norm(norm_a, res_a, y, wn, 1e-6)
+        res_b = res0.to(dev).clone()
+        norm_b, res_b2 = lin.forward_reduce_norm(x_shard, res_b, wn, 1e-6)
+        torch.cuda.synchronize()
+        assert res_b2.data_ptr() == res_b.data_ptr()
+        assert torch.equal(res_a, res_b) and torch.equal(norm_a, norm_b), f"row-parallel linear tail T={T}"
+        full = x_full.float() @ w_full.float().t() + (b_full.float() if use_bias else 0.0)
+        assert O.rel_l2(y.cpu(), full.to(torch.bfloat16)) <= 1e-2
+    assert ops.read_status(dev) == 0
+
     # ---- 6. fp8 experts, tensor parallel with I/tp = 192 (slices split the 128-wide scale blocks), k-slot sum fused
     # with the all-reduce: against the all-reduced per-rank CPU emulations
     g = torch.Generator().manual_seed(91)
@@ -278,17 +313,19 @@ def main():
     mine = [per_rank[rank].to(dev) for per_rank in c3s]
     outs = torch.empty(reps, T, H, dtype=torch.bfloat16, device=dev)
     stream = torch.cuda.current_stream().cuda_stream
-    dist.barrier()
-    for i in range(reps):
-        if (i + rank) % 7 == 0:
-            torch.cuda._sleep(200_000 * (1 + rank))   # this rank falls behind its peers for a while
-        check(lib.moe_b200_ar_moe_sum_all_reduce(comm._ptr, mine[i % 3].data_ptr(), outs[i].data_ptr(), T, k, H,
-                                                 comm.buffer_ptrs[rank], comm.max_size, 0,
-                                                 ops.status_word(dev).data_ptr(), stream))
-    torch.cuda.synchronize()
-    assert ops.read_status(dev) == 0
-    for i in range(reps):
-        assert torch.equal(outs[i].cpu(), wants[i % 3]), f"one-barrier all-reduce, call {i}"
+    for algo in (0, 3):  # the flag-in-data kernel, then the one-barrier kernel
+        outs.zero_()
+        dist.barrier()
+        for i in range(reps):
+            if (i + rank) % 7 == 0:
+                torch.cuda._sleep(200_000 * (1 + rank))   # this rank falls behind its peers for a while
+            check(lib.moe_b200_ar_moe_sum_all_reduce(comm._ptr, mine[i % 3].data_ptr(), outs[i].data_ptr(), T, k, H,
+                                                     comm.buffer_ptrs[rank], comm.max_size, algo,
+                                                     ops.status_word(dev).data_ptr(), stream))
+        torch.cuda.synchronize()
+        assert ops.read_status(dev) == 0
+        for i in range(reps):
+            assert torch.equal(outs[i].cpu(), wants[i % 3]), f"barrier-free / one-barrier all-reduce (algo {algo}), call {i}"
     c3_buf = mine[0].clone()
     out_g = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
     side = torch.cuda.Stream()
@@ -309,6 +346,83 @@ def main():
         assert torch.equal(out_g.cpu(), wants[i % 3]), f"one-barrier all-reduce, graph replay {i}"
         dist.barrier()
     assert ops.read_status(dev) == 0
+
+    # ---- 8. inside the reference's own caller: its Qwen3MoeSparseMoeBlock (gate linear -> FusedMoE -> reduce,
+    # nanovllm/models/qwen3_moe.py:66-116) built tensor-parallel on these ranks from the staged copy of the reference,
+    # run as it is (its Triton experts; the reduction by NCCL) and with this library's fused_topk / fused_experts /
+    # tensor_model_parallel_all_reduce patched into its modules; then the patched block captured into a CUDA graph
+    # under capture() as the reference's model runner does (qwen3_moe.py:710-759) and replayed on new tokens
+    from oracle.build_ref import load_reference_package
+    if load_reference_package() is not None:
+        import nanovllm.layers.for_moe.fused_moe as rfm
+        import nanovllm.layers.fused_moe as rlayer
+        import nanovllm.models.qwen3_moe as rmodel
+        from transformers import Qwen3MoeConfig
+        cfg = Qwen3MoeConfig(hidden_size=1024, num_experts=32, num_experts_per_tok=4, moe_intermediate_size=96 * world,
+                             norm_topk_prob=True)
+        saved = torch.get_default_dtype()
+        torch.set_default_dtype(torch.bfloat16)
+        try:
+            with torch.device(dev):
+                blk = rmodel.Qwen3MoeSparseMoeBlock(cfg)
+        finally:
+            torch.set_default_dtype(saved)
+        E, I, H = cfg.num_experts, cfg.moe_intermediate_size, cfg.hidden_size
+        assert blk.experts.tp_size == world and blk.experts.w13_weight.shape == (E, 2 * I // world, H)
+        g = torch.Generator().manual_seed(123)
+        for e in range(E):
+            gate = (torch.randn(I, H, generator=g) * 0.05).to(torch.bfloat16).to(dev)
+            up = (torch.randn(I, H, generator=g) * 0.05).to(torch.bfloat16).to(dev)
+            down = (torch.randn(H, I, generator=g) * 0.05).to(torch.bfloat16).to(dev)
+            blk.experts.weight_loader(blk.experts.w13_weight, gate, "experts.w13_weight", "w1", e)
+            blk.experts.weight_loader(blk.experts.w13_weight, up, "experts.w13_weight", "w3", e)
+            blk.experts.weight_loader(blk.experts.w2_weight, down, "experts.w2_weight", "w2", e)
+        blk.gate.weight.data.copy_((torch.randn(E, H, generator=g) * 0.02).to(torch.bfloat16))
+        xs = [torch.randn(T_, H, generator=g).to(torch.bfloat16).to(dev) for T_ in (64, 64, 1536)]
+
+        def nccl_sum(t):
+            dist.all_reduce(t)
+            return t
+
+        stock_fns = (rfm.fused_topk, blk.experts.quant_method.fused_experts, rlayer.tensor_model_parallel_all_reduce)
+        try:
+            rlayer.tensor_model_parallel_all_reduce = nccl_sum
+            wants = [blk(x_.clone()) for x_ in xs]
+            torch.cuda.synchronize()
+            rfm.fused_topk = fused_moe.fused_topk
+            blk.experts.quant_method.fused_experts = fused_moe.fused_experts
+            rlayer.tensor_model_parallel_all_reduce = car.tensor_model_parallel_all_reduce
+            l0 = ops.launch_count()
+            gots = [blk(x_.clone()) for x_ in xs]
+            torch.cuda.synchronize()
+            assert ops.launch_count() - l0 >= 4 * len(xs), "the patched block did not run this library's kernels"
+            for got, want in zip(gots, wants):
+                rl, ma = O.rel_l2(got.cpu(), want.cpu()), O.max_abs(got.cpu(), want.cpu())
+                assert rl <= 5e-3 and ma <= max(2e-2, 2 ** -7 * float(want.float().abs().max())), (rl, ma)
+            # graph capture of the patched block on a fixed input buffer
+            x_buf = xs[0].clone()
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                with car.capture():
+                    blk(x_buf.clone())  # warm-up outside the capture
+                    graph = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(graph, stream=side):
+                        res = blk(x_buf.clone())
+            torch.cuda.current_stream().wait_stream(side)
+            dist.barrier()
+            for i in (1, 0):
+                x_buf.copy_(xs[i])
+                torch.cuda.synchronize()
+                dist.barrier()
+                graph.replay()
+                torch.cuda.synchronize()
+                assert torch.equal(res, gots[i]), f"graph replay of the patched block, input {i}"
+                dist.barrier()
+        finally:
+            rfm.fused_topk, blk.experts.quant_method.fused_experts, rlayer.tensor_model_parallel_all_reduce = stock_fns
+        assert ops.read_status(dev) == 0
+        print(f"TP_WORKER_REFERENCE_CALLER_OK rank={rank}", flush=True)
 
     dist.barrier()
     comm.close()
