@@ -68,7 +68,7 @@ def recorded_traffic(workload_name: str):
 class ClockSampler:
     """Samples SM clock, power and clock-event reasons through NVML (read-only) while the GPU works."""
 
-    def __init__(self, index: int, period_s: float = 0.02):
+    def __init__(self, index: int, period_s: float = 0.01):
         self.samples = []
         self.period = period_s
         self._stop = threading.Event()
@@ -156,8 +156,7 @@ def build_parser():
     ap.add_argument("--no-reference-gpu", action="store_true",
                     help="skip timing the reference's own Triton path from oracle/_ref (1 GPU)")
     ap.add_argument("--rounds", type=int, default=None,
-                    help="how many times the K-step region is timed (default: at least 25, more for short regions); "
-                         "the median round is reported")
+                    help="how many times the K-step region is timed (default 25); the median round is reported")
     ap.add_argument("--only-steps", action="store_true",
                     help="stop after the timed steps (no e2e, roofline or comparison legs): for ncu launch lists")
     return ap
@@ -471,9 +470,7 @@ def run_workload(ctx: Ctx, wl, steps: int, warmup: int, primary: bool, mixed: bo
     launches = int(lib.moe_b200_launch_count() - launches0)
     if use_graph:
         launches = launches_per_graph * steps  # replayed kernels are not seen by the library's launch counter
-    rounds = args.rounds if args.rounds else min(200, max(25, int(1000.0 / max(round_ms[0], 1e-3)) + 1))
-    if not primary:
-        rounds = min(rounds, 25)
+    rounds = args.rounds if args.rounds else 25
     for _ in range(rounds - 1):
         round_ms.append(one_round())
     t_wall1 = time.perf_counter()
@@ -710,9 +707,14 @@ def all_reduce_legs(ctx: Ctx, wl, rec, st):
             check(lib.moe_b200_ar_moe_sum_all_reduce(comm._ptr, c3.data_ptr(), res.data_ptr(), t_ar, wl.top_k, wl.H,
                                                      comm.buffer_ptrs[rank], comm.max_size, 0, stw,
                                                      torch.cuda.current_stream().cuda_stream))
+        def fused_barriers(i=0):  # algo 3: the same reduction kept off the flag-in-data path
+            check(lib.moe_b200_ar_moe_sum_all_reduce(comm._ptr, c3.data_ptr(), res.data_ptr(), t_ar, wl.top_k, wl.H,
+                                                     comm.buffer_ptrs[rank], comm.max_size, 3, stw,
+                                                     torch.cuda.current_stream().cuda_stream))
         legs = {"all_reduce_staged": plain}
         if c3 is not None:
             legs["k_slot_sum_all_reduce"] = fused
+            legs["k_slot_sum_all_reduce_with_barriers"] = fused_barriers
         entry = {}
         for label, fn in legs.items():
             run, how = fn, "eager"

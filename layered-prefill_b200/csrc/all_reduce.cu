@@ -41,12 +41,14 @@ constexpr int kMaxRanks = 8;
 constexpr int kMaxArBlocks = 160;  // up to one block per SM (148 on B200) for large messages
 constexpr int kArThreads = 512;
 constexpr int kFusedBlocks = 32;  // fixed grid of the barrier-saving one-shot kernel (its per-block call counters rely on it)
+constexpr int kLLBlocks = 64;     // fixed grid of the flag-in-data kernel (same reason), 256 threads each
+constexpr int kLLThreads = 256;
 
 struct alignas(128) Signal {
   uint32_t arrive[kMaxArBlocks][kMaxRanks];  // arrive[b][r]: written by block b of rank r
   uint32_t epoch[kMaxArBlocks];              // this rank's barrier count per block
   uint32_t fused_calls[kFusedBlocks];        // this rank's count of barrier-saving one-shot calls, per block
-  uint32_t ll_calls[kFusedBlocks];           // this rank's count of flag-in-data one-shot calls, per block
+  uint32_t ll_calls[kLLBlocks];              // this rank's count of flag-in-data one-shot calls, per block
 };
 constexpr size_t kMetaBytes = (sizeof(Signal) + 255) / 256 * 256;
 
@@ -295,8 +297,12 @@ __device__ __forceinline__ uint4 ld_ll(const uint4* src) {
   return v;
 }
 
+// Index of vector v's first packet inside a slot (the second one is 32 packets further): vectors are taken in groups
+// of 32 (one per lane), a group owns 64 consecutive packets.
+__device__ __forceinline__ long long ll_packet(long long v) { return (v & ~31ll) * 2 + (v & 31ll); }
+
 template <int N>
-__global__ void __launch_bounds__(kArThreads, 1) ar_ll_sum_kernel(const ArParams p, const LLParams ll) {
+__global__ void __launch_bounds__(kLLThreads, 1) ar_ll_sum_kernel(const ArParams p, const LLParams ll) {
   grid_dependency_launch();
   grid_dependency_wait();
   const uint32_t epoch = p.self_sg->ll_calls[blockIdx.x] + 1u;
@@ -320,11 +326,13 @@ __global__ void __launch_bounds__(kArThreads, 1) ar_ll_sum_kernel(const ArParams
     }
     Vec16 o;
     VecTraits<__nv_bfloat16>::pack(o, acc);
-    const long long slot = (parity_off + static_cast<long long>(p.rank) * ll.slot_vecs + v) * 2;
+    // packets of the warp's 32 vectors: first halves in 32 consecutive packets, second halves in the next 32, so
+    // that each store instruction of the warp covers 512 contiguous bytes of the peer's memory
+    const long long slot = (parity_off + static_cast<long long>(p.rank) * ll.slot_vecs) * 2 + ll_packet(v);
 #pragma unroll
     for (int r = 0; r < N; ++r) {
       st_ll(area[r] + slot, o.u.x, o.u.y, epoch);
-      st_ll(area[r] + slot + 1, o.u.z, o.u.w, epoch);
+      st_ll(area[r] + slot + 32, o.u.z, o.u.w, epoch);
     }
   }
   // receive: poll this rank's own area until every rank's packets of this call are there
@@ -342,9 +350,9 @@ __global__ void __launch_bounds__(kArThreads, 1) ar_ll_sum_kernel(const ArParams
       bool all = true;
 #pragma unroll
       for (int r = 0; r < N; ++r) {
-        const long long slot = (parity_off + static_cast<long long>(r) * ll.slot_vecs + v) * 2;
+        const long long slot = (parity_off + static_cast<long long>(r) * ll.slot_vecs) * 2 + ll_packet(v);
         lo[r] = ld_ll(mine + slot);
-        hi[r] = ld_ll(mine + slot + 1);
+        hi[r] = ld_ll(mine + slot + 32);
         all = all && lo[r].y == epoch && lo[r].w == epoch && hi[r].y == epoch && hi[r].w == epoch;
       }
       if (all) break;
@@ -610,7 +618,7 @@ int ar_moe_sum_all_reduce_impl(int64_t handle, const void* c3, void* out, int T,
   if (oneshot && algo != 3 && ll_slot_vecs >= bytes / 16) {
     LLParams ll{c->ll_rd, ll_slot_vecs};
 #define MOE_B200_ARL_CASE(n) \
-  case n: launch_pdl(ar_ll_sum_kernel<n>, dim3(kFusedBlocks), dim3(kArThreads), 0, stream, p, ll); break;
+  case n: launch_pdl(ar_ll_sum_kernel<n>, dim3(kLLBlocks), dim3(kLLThreads), 0, stream, p, ll); break;
     switch (c->world) {
       MOE_B200_ARL_CASE(2)
       MOE_B200_ARL_CASE(4)

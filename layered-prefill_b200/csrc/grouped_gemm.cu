@@ -162,6 +162,35 @@ __device__ __forceinline__ void epilogue_rows(const KernelParams& p, uint32_t ta
   } else {
     const __nv_bfloat16* bias_d = p.bias ? p.bias + static_cast<long long>(e) * p.out_cols : nullptr;
     const int lane = threadIdx.x & 31;
+    if (__popc(__ballot_sync(0xffffffffu, valid)) <= 8) {
+      // decode-sized batches: a handful of live rows among the 32 of this warp. Each live lane converts and
+      // stores its own row; turning all 32 rows around in shared memory would cost more than it saves.
+      // Four TMEM loads (64 columns) per wait: with a short K the tile's main loop is a thousand cycles and a
+      // wait per 16 columns made this epilogue the longest stage of the pipeline.
+      __nv_bfloat16* out_row = p.out + static_cast<long long>(valid ? flat : 0) * p.out_ld;
+      for (int c0 = 0; c0 < p.tile_cols; c0 += 64) {
+        uint32_t d[4][16];
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) tmem_ld_x16(taddr + c0 + 16 * q4, d[q4]);
+        tmem_ld_wait();
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          const int col = n0 + c0 + 16 * q4;
+          if (valid && c0 + 16 * q4 < p.tile_cols && col < p.out_cols) {
+            Pack8 o[2];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              float v = __uint_as_float(d[q4][j]);
+              if (bias_d) v += __bfloat162float(bias_d[col + j]);
+              o[j >> 3].h[j & 7] = __float2bfloat16_rn(v * w);
+            }
+            *reinterpret_cast<uint4*>(out_row + col) = o[0].u;
+            *reinterpret_cast<uint4*>(out_row + col + 8) = o[1].u;
+          }
+        }
+      }
+      return;
+    }
     const uint32_t patch_w = patch + static_cast<uint32_t>(lane) * 128u;  // this lane's row of the patch
     const int chunk = lane & 7;   // read side: 16-byte piece of a row
     const int rsub = lane >> 3;   // read side: row inside a group of four
@@ -250,10 +279,14 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b, const KernelPara
     if (lane == 0) {
       uint32_t s = 0, ph = 0;
       bool ok = true;
+      // the expert of the next tile is fetched while this tile's loads are issued: with a short K (a rank's slice
+      // of I in the down pass) a tile is a few stages, and a dependent global load per tile would show
+      int e_next = static_cast<int>(blockIdx.x) < total_tiles ? p.expert_ids[blockIdx.x / p.n_tiles] : 0;
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
         const int m_blk = tile / p.n_tiles;
         const int n0 = (tile % p.n_tiles) * p.tile_cols;
-        const int e = p.expert_ids[m_blk];
+        const int e = e_next;
+        if (tile + static_cast<int>(gridDim.x) < total_tiles) e_next = p.expert_ids[(tile + gridDim.x) / p.n_tiles];
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&bar_empty[s], ph ^ 1u)) {
             report(p.status, kErrWaitEmpty);
@@ -379,12 +412,22 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b, const KernelPara
     const uint32_t swz = static_cast<uint32_t>((ch ^ (row0 & 7)) << 4);
     uint32_t s = 0, ph = 0;
     bool ok = true;
+    // the permutation entries of the next tile are fetched one tile ahead (same reason as in the producer)
+    int flat_next[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      flat_next[i] = static_cast<int>(blockIdx.x) < total_tiles
+                         ? p.sorted_ids[static_cast<long long>(blockIdx.x / p.n_tiles) * BM + row0 + 16 * i]
+                         : p.numel;
     for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
       const int m_blk = tile / p.n_tiles;
       const __nv_bfloat16* src[8];
+      const bool more = tile + static_cast<int>(gridDim.x) < total_tiles;
+      const long long next_base = more ? static_cast<long long>((tile + gridDim.x) / p.n_tiles) * BM + row0 : 0;
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        const int flat = p.sorted_ids[static_cast<long long>(m_blk) * BM + row0 + 16 * i];
+        const int flat = flat_next[i];
+        if (more) flat_next[i] = p.sorted_ids[next_base + 16 * i];
         if (kMode == 1)
           src[i] = flat < p.numel ? p.x + static_cast<long long>(flat / p.top_k) * p.K + ch * 8 : nullptr;
         else  // down pass: row p of the permuted intermediate

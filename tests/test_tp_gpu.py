@@ -16,8 +16,11 @@ def _run(world: int, port: int):
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=900, env=env)
     assert r.returncode == 0, r.stdout[-3000:] + "\n" + r.stderr[-6000:]
+    staged = os.path.exists(os.path.join(ROOT, "oracle", "_ref", "nanovllm", "__init__.py"))
     for rank in range(world):
         assert f"TP_WORKER_OK rank={rank}" in r.stdout
+        if staged:  # the section that runs inside the reference's own sparse MoE block must not have been skipped
+            assert f"TP_WORKER_REFERENCE_CALLER_OK rank={rank}" in r.stdout, r.stdout[-2000:]
 
 
 @pytest.mark.parametrize("world", [2, 4, 8])

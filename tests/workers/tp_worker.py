@@ -349,7 +349,7 @@ def main():
 
     # ---- 8. inside the reference's own caller: its Qwen3MoeSparseMoeBlock (gate linear -> FusedMoE -> reduce,
     # nanovllm/models/qwen3_moe.py:66-116) built tensor-parallel on these ranks from the staged copy of the reference,
-    # run as it is (its Triton experts; the reduction by NCCL) and with this library's fused_topk / fused_experts /
+    # run as it is (its Triton experts; its reduction's arithmetic carried by NCCL) and with this library's fused_topk / fused_experts /
     # tensor_model_parallel_all_reduce patched into its modules; then the patched block captured into a CUDA graph
     # under capture() as the reference's model runner does (qwen3_moe.py:710-759) and replayed on new tokens
     from oracle.build_ref import load_reference_package
@@ -381,8 +381,14 @@ def main():
         xs = [torch.randn(T_, H, generator=g).to(torch.bfloat16).to(dev) for T_ in (64, 64, 1536)]
 
         def nccl_sum(t):
-            dist.all_reduce(t)
-            return t
+            # the arithmetic of the reference's own all-reduce kernel (fp32 sum in rank order, one rounding,
+            # csrc/custom_all_reduce.cuh:288-296), carried by NCCL: gather the partial sums, add them here
+            parts = [torch.empty_like(t) for _ in range(world)]
+            dist.all_gather(parts, t.contiguous())
+            acc = parts[0].float()
+            for part in parts[1:]:
+                acc += part.float()
+            return acc.to(t.dtype)
 
         stock_fns = (rfm.fused_topk, blk.experts.quant_method.fused_experts, rlayer.tensor_model_parallel_all_reduce)
         try:
