@@ -374,18 +374,35 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b, const KernelPara
     const int q = warp & 3;  // TMEM lane quarter this warp may read
     const int row_in_tile = q * 32 + lane;
     const uint32_t patch = smem_u32(ring) + num_stages * stage_bytes + static_cast<uint32_t>(q) * kPatchBytes;
+    // A tile's permutation entry, routed weight and expert come from global memory, the weight through the entry.
+    // These warps handle the tiles one after the other, so with a short main loop (a rank's slice of I in the down
+    // pass: two K blocks) two dependent loads at the head of every tile would set the pace of the whole kernel:
+    // the entry is fetched two tiles ahead, the weight and the expert one tile ahead.
+    const int step = static_cast<int>(gridDim.x);
+    auto load_flat = [&](int tile) {
+      return tile < total_tiles ? p.sorted_ids[static_cast<long long>(tile / p.n_tiles) * BM + row_in_tile] : p.numel;
+    };
+    auto load_expert = [&](int tile) { return tile < total_tiles ? p.expert_ids[tile / p.n_tiles] : 0; };
+    int flat_cur = load_flat(blockIdx.x);
+    int flat_nx = load_flat(static_cast<int>(blockIdx.x) + step);
+    int e_cur = load_expert(blockIdx.x);
+    float w_cur = (kMode == 2 && flat_cur < p.numel) ? p.topk_w[flat_cur] : 0.f;
     uint32_t tile_iter = 0;
-    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++tile_iter) {
+    for (int tile = blockIdx.x; tile < total_tiles; tile += step, ++tile_iter) {
       const uint32_t acc = tile_iter & 1u;
       const uint32_t acc_ph = (tile_iter >> 1) & 1u;
       const int m_blk = tile / p.n_tiles;
       const int n0 = (tile % p.n_tiles) * p.tile_cols;
-      const int e = p.expert_ids[m_blk];
+      const int e = e_cur;
       const long long pos = static_cast<long long>(m_blk) * BM + row_in_tile;
-      const int flat = p.sorted_ids[pos];
+      const int flat = flat_cur;
       const bool valid = flat < p.numel;
-      float w = 0.f;
-      if (kMode == 2 && valid) w = p.topk_w[flat];
+      const float w = w_cur;
+      // prefetch for the next tiles (consumed after this tile's epilogue)
+      flat_cur = flat_nx;
+      w_cur = (kMode == 2 && flat_nx < p.numel) ? p.topk_w[flat_nx] : 0.f;
+      e_cur = load_expert(tile + step);
+      flat_nx = load_flat(tile + 2 * step);
 
       bool ok = mbar_wait(&bar_tmem_full[acc], acc_ph);
       ok = __all_sync(0xffffffffu, ok);
