@@ -50,7 +50,8 @@ constexpr int kAccCols = 256;
 constexpr int kTmemCols = 512;
 constexpr int kBarrierBytes = 1024;                      // barriers + TMEM slot, in front of the ring
 constexpr int kSmemLimit = 227 * 1024;                   // opt-in shared memory per CTA on sm_100
-constexpr int kPatchBytes = 32 * 128;                    // per epilogue warp (down pass): 32 rows x 64 bf16 columns
+constexpr int kPatchBytes = 32 * 128;                    // one transposition patch (down pass): 32 rows x 64 bf16 columns
+constexpr int kPatchesPerWarp = 2;                       // used in turn by each epilogue warp
 constexpr int kRingBudget = kSmemLimit - kBarrierBytes - 1024 /*alignment slack*/;
 
 constexpr int kWarpTma = 0;
@@ -191,13 +192,20 @@ __device__ __forceinline__ void epilogue_rows(const KernelParams& p, uint32_t ta
       }
       return;
     }
-    const uint32_t patch_w = patch + static_cast<uint32_t>(lane) * 128u;  // this lane's row of the patch
+    // Two patches per warp, used in turn, and the TMEM loads of the next 64 columns issued as soon as the current
+    // ones are converted: TMEM latency, shared-memory round trip and global stores of neighbouring chunks overlap.
     const int chunk = lane & 7;   // read side: 16-byte piece of a row
     const int rsub = lane >> 3;   // read side: row inside a group of four
-    for (int c0 = 0; c0 < p.tile_cols; c0 += 64) {
-      uint32_t d[4][16];
+    int flat_r[8];                // flat index of the eight rows this lane stores pieces of
 #pragma unroll
-      for (int q4 = 0; q4 < 4; ++q4) tmem_ld_x16(taddr + c0 + 16 * q4, d[q4]);
+    for (int i = 0; i < 8; ++i) flat_r[i] = __shfl_sync(0xffffffffu, flat, rsub + 4 * i);
+    uint32_t d[4][16];
+#pragma unroll
+    for (int q4 = 0; q4 < 4; ++q4) tmem_ld_x16(taddr + 16 * q4, d[q4]);
+    int buf = 0;
+    for (int c0 = 0; c0 < p.tile_cols; c0 += 64, buf ^= 1) {
+      const uint32_t patch_b = patch + static_cast<uint32_t>(buf) * kPatchBytes;
+      const uint32_t patch_w = patch_b + static_cast<uint32_t>(lane) * 128u;  // this lane's row of the patch
       tmem_ld_wait();
       const int col0 = n0 + c0;
 #pragma unroll
@@ -213,17 +221,20 @@ __device__ __forceinline__ void epilogue_rows(const KernelParams& p, uint32_t ta
         st_shared_v4(patch_w + (static_cast<uint32_t>((2 * q4) ^ (lane & 7)) << 4), o[0].u);
         st_shared_v4(patch_w + (static_cast<uint32_t>((2 * q4 + 1) ^ (lane & 7)) << 4), o[1].u);
       }
-      __syncwarp();
+      if (c0 + 64 < p.tile_cols) {
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) tmem_ld_x16(taddr + c0 + 64 + 16 * q4, d[q4]);
+      }
+      __syncwarp();  // this patch is complete. (Its previous contents were read two chunks ago: every lane finished
+                     // those reads before it arrived at the barrier of the chunk in between.)
       const int col = col0 + chunk * 8;
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         const int r = rsub + 4 * i;
-        const int flat_r = __shfl_sync(0xffffffffu, flat, r);
-        const uint4 v = ld_shared_v4(patch + static_cast<uint32_t>(r) * 128u + (static_cast<uint32_t>(chunk ^ (r & 7)) << 4));
-        if (flat_r < p.numel && col < p.out_cols)
-          *reinterpret_cast<uint4*>(p.out + static_cast<long long>(flat_r) * p.out_ld + col) = v;
+        const uint4 v = ld_shared_v4(patch_b + static_cast<uint32_t>(r) * 128u + (static_cast<uint32_t>(chunk ^ (r & 7)) << 4));
+        if (flat_r[i] < p.numel && col < p.out_cols)
+          *reinterpret_cast<uint4*>(p.out + static_cast<long long>(flat_r[i]) * p.out_ld + col) = v;
       }
-      __syncwarp();  // the patch is rewritten by the next 64 columns
     }
   }
 }
@@ -373,7 +384,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b, const KernelPara
     // ------------------------------------------------------------------ epilogue
     const int q = warp & 3;  // TMEM lane quarter this warp may read
     const int row_in_tile = q * 32 + lane;
-    const uint32_t patch = smem_u32(ring) + num_stages * stage_bytes + static_cast<uint32_t>(q) * kPatchBytes;
+    const uint32_t patch = smem_u32(ring) + num_stages * stage_bytes + static_cast<uint32_t>(q) * (kPatchesPerWarp * kPatchBytes);
     // A tile's permutation entry, routed weight and expert come from global memory, the weight through the entry.
     // These warps handle the tiles one after the other, so with a short main loop (a rank's slice of I in the down
     // pass: two K blocks) two dependent loads at the head of every tile would set the pace of the whole kernel:
@@ -513,8 +524,11 @@ int pick_gate_up_tile(int inter, double m_blocks) {
   return 0;
 }
 
-int pick_down_tile(int hidden, double m_blocks) {
+int pick_down_tile(int hidden, int inter, double m_blocks) {
   if (hidden <= 128) return (hidden + 15) / 16 * 16;
+  // a rank's thin slice of I: a tile's main loop is a few K blocks and per-tile costs set the pace, so fewer,
+  // wider tiles win whatever the wave count says
+  if (inter <= 256) return 256;
   const int sms = device_sm_count();
   const double e256 = wave_efficiency(m_blocks * ((hidden + 255) / 256), sms);
   const double e128 = wave_efficiency(m_blocks * ((hidden + 127) / 128), sms);
@@ -645,7 +659,7 @@ int launch_grouped_gemm2(const GroupedGemmArgs& a, const __nv_bfloat16* h_sorted
   if (int st = check_common(a)) return st;
   if (a.numel == 0 || a.max_m_blocks == 0) return kStatusOk;
   if (a.hidden % 16 != 0) return set_error(kStatusInvalidArgument, "grouped GEMM down: hidden must be a multiple of 16");
-  const int tile_cols = pick_down_tile(a.hidden, expected_m_blocks(a.numel, a.top_k, a.num_experts));
+  const int tile_cols = pick_down_tile(a.hidden, a.inter, expected_m_blocks(a.numel, a.top_k, a.num_experts));
   if (int st = ensure_smem_attr<2>()) return st;
 
   CUtensorMap map_b;
@@ -661,11 +675,11 @@ int launch_grouped_gemm2(const GroupedGemmArgs& a, const __nv_bfloat16* h_sorted
   p.out_cols = a.hidden; p.inter = a.inter; p.interleaved = 0;
   p.out = c3; p.out_ld = a.hidden; p.topk_w = topk_w; p.bias = w2_bias;
   p.alpha = 0.f; p.limit = 0.f; p.status = a.status;
-  pick_ring(p.mma_n, 4 * kPatchBytes, &p.stages, &p.stage_bytes);
+  pick_ring(p.mma_n, 4 * kPatchesPerWarp * kPatchBytes, &p.stages, &p.stage_bytes);
 
   long long tiles = static_cast<long long>(a.max_m_blocks) * p.n_tiles;
   const int grid = static_cast<int>(tiles < device_sm_count() ? tiles : device_sm_count());
-  const int smem_bytes = kBarrierBytes + 1024 + p.stages * p.stage_bytes + 4 * kPatchBytes;
+  const int smem_bytes = kBarrierBytes + 1024 + p.stages * p.stage_bytes + 4 * kPatchesPerWarp * kPatchBytes;
   if (int st = check_cuda(launch_pdl(grouped_gemm_kernel<2>, dim3(grid), dim3(kThreads), smem_bytes, stream, map_b, p),
                           "grouped_gemm down launch"))
     return st;
