@@ -221,3 +221,68 @@ def test_library_patched_into_the_reference_sparse_moe_block(ref, single_rank_gr
         torch.cuda.synchronize()
         assert ops.read_status(d) == 0
         _bounds(got.cpu(), want.cpu(), f"patched sparse MoE block, T={T}", scaled=True)
+
+
+def test_reference_safetensors_loader_fills_this_librarys_layers(ref, single_rank_group, tmp_path):
+    """The reference's own checkpoint loader (nanovllm/utils/loader.py:37-116: name pattern -> parameter, shard id and
+    expert id -> `moe_layer.weight_loader(...)`; every other tensor through its parameter's `weight_loader`) driven
+    over a synthetic Qwen3-MoE-named safetensors file into a module tree built from THIS library's FusedMoE and
+    RowParallelLinear: the loaded parameters must be the checkpoint's tensors in the reference's layout."""
+    import nanovllm.utils.loader as rloader
+    from safetensors.torch import save_file
+    from torch import nn
+    from layered_prefill_b200.layer import FusedMoE
+    from layered_prefill_b200.linear import RowParallelLinear
+    E, k, H, I, L = 4, 2, 64, 32, 2
+
+    class Mlp(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.experts = FusedMoE(E, k, H, I, params_dtype=torch.bfloat16)
+            self.gate = nn.Linear(H, E, bias=False, dtype=torch.bfloat16)
+
+    class Attn(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.o_proj = RowParallelLinear(H, H).to(torch.bfloat16)
+
+    class Layer(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.mlp, self.self_attn = Mlp(), Attn()
+
+    class Inner(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.layers = nn.ModuleList([Layer() for _ in range(L)])
+
+    class Model(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.model = Inner()
+
+    model = Model()
+    g = torch.Generator().manual_seed(77)
+    ckpt = {}
+    for li in range(L):
+        for e in range(E):
+            for proj, shape in (("gate_proj", (I, H)), ("up_proj", (I, H)), ("down_proj", (H, I))):
+                ckpt[f"model.layers.{li}.mlp.experts.{e}.{proj}.weight"] = torch.randn(*shape, generator=g).to(torch.bfloat16)
+        ckpt[f"model.layers.{li}.mlp.gate.weight"] = torch.randn(E, H, generator=g).to(torch.bfloat16)
+        ckpt[f"model.layers.{li}.self_attn.o_proj.weight"] = torch.randn(H, H, generator=g).to(torch.bfloat16)
+    save_file(ckpt, str(tmp_path / "model.safetensors"))
+    saved = rloader.FusedMoE
+    rloader.FusedMoE = FusedMoE  # the loader finds MoE layers by isinstance
+    try:
+        rloader.load_model(model, str(tmp_path))
+    finally:
+        rloader.FusedMoE = saved
+    for li in range(L):
+        layer = model.model.layers[li]
+        for e in range(E):
+            pre = f"model.layers.{li}.mlp.experts.{e}."
+            assert torch.equal(layer.mlp.experts.w13_weight[e, :I], ckpt[pre + "gate_proj.weight"])
+            assert torch.equal(layer.mlp.experts.w13_weight[e, I:], ckpt[pre + "up_proj.weight"])
+            assert torch.equal(layer.mlp.experts.w2_weight[e], ckpt[pre + "down_proj.weight"])
+        assert torch.equal(layer.mlp.gate.weight, ckpt[f"model.layers.{li}.mlp.gate.weight"])
+        assert torch.equal(layer.self_attn.o_proj.weight, ckpt[f"model.layers.{li}.self_attn.o_proj.weight"])
