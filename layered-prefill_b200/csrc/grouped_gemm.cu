@@ -56,9 +56,9 @@ constexpr int kRingBudget = kSmemLimit - kBarrierBytes - 1024 /*alignment slack*
 
 constexpr int kWarpTma = 0;
 constexpr int kWarpMma = 1;
-constexpr int kWarpEpilogue0 = 2;  // 4 warps
-constexpr int kWarpGather0 = 6;    // 4 warps: token rows by cp.async
-constexpr int kThreads = 320;
+constexpr int kWarpEpilogue0 = 2;  // kEpiWarps warps (4, or 8 for thin K: two per TMEM lane quarter, half the columns each)
+// after them kGatherWarps warps (4, or 2) bring the token rows in by cp.async
+constexpr int role_threads(int epi_warps, int gather_warps) { return 32 * (2 + epi_warps + gather_warps); }
 
 struct KernelParams {
   const int* sorted_ids;
@@ -93,10 +93,12 @@ __device__ __forceinline__ void report(int* status, int code) { atomicCAS(status
 
 // Epilogue of one 128-row tile for the 32 rows one warp may read from TMEM (taddr = its lane quarter and
 // the accumulator's first column). pos = permuted row, flat = t*k+j of that row (>= numel on padding rows);
-// patch = shared-memory address of this warp's 4 KB transposition patch (down pass only).
+// patch = shared-memory address of this warp's transposition patches, [c_begin, c_end) = the tile columns this
+// warp handles (down pass only; the gate_up pass always takes the whole tile).
 template <int kMode>
 __device__ __forceinline__ void epilogue_rows(const KernelParams& p, uint32_t taddr, long long pos, int flat,
-                                              bool valid, float w, int e, int n0, uint32_t patch) {
+                                              bool valid, float w, int e, int n0, uint32_t patch, int c_begin,
+                                              int c_end) {
   if (kMode == 1) {
     __nv_bfloat16* out_row = p.out + pos * p.out_ld;
     if (!p.interleaved) {
@@ -169,7 +171,7 @@ __device__ __forceinline__ void epilogue_rows(const KernelParams& p, uint32_t ta
       // Four TMEM loads (64 columns) per wait: with a short K the tile's main loop is a thousand cycles and a
       // wait per 16 columns made this epilogue the longest stage of the pipeline.
       __nv_bfloat16* out_row = p.out + static_cast<long long>(valid ? flat : 0) * p.out_ld;
-      for (int c0 = 0; c0 < p.tile_cols; c0 += 64) {
+      for (int c0 = c_begin; c0 < c_end; c0 += 64) {
         uint32_t d[4][16];
 #pragma unroll
         for (int q4 = 0; q4 < 4; ++q4) tmem_ld_x16(taddr + c0 + 16 * q4, d[q4]);
@@ -177,7 +179,7 @@ __device__ __forceinline__ void epilogue_rows(const KernelParams& p, uint32_t ta
 #pragma unroll
         for (int q4 = 0; q4 < 4; ++q4) {
           const int col = n0 + c0 + 16 * q4;
-          if (valid && c0 + 16 * q4 < p.tile_cols && col < p.out_cols) {
+          if (valid && c0 + 16 * q4 < c_end && col < p.out_cols) {
             Pack8 o[2];
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
@@ -201,9 +203,9 @@ __device__ __forceinline__ void epilogue_rows(const KernelParams& p, uint32_t ta
     for (int i = 0; i < 8; ++i) flat_r[i] = __shfl_sync(0xffffffffu, flat, rsub + 4 * i);
     uint32_t d[4][16];
 #pragma unroll
-    for (int q4 = 0; q4 < 4; ++q4) tmem_ld_x16(taddr + 16 * q4, d[q4]);
+    for (int q4 = 0; q4 < 4; ++q4) tmem_ld_x16(taddr + c_begin + 16 * q4, d[q4]);
     int buf = 0;
-    for (int c0 = 0; c0 < p.tile_cols; c0 += 64, buf ^= 1) {
+    for (int c0 = c_begin; c0 < c_end; c0 += 64, buf ^= 1) {
       const uint32_t patch_b = patch + static_cast<uint32_t>(buf) * kPatchBytes;
       const uint32_t patch_w = patch_b + static_cast<uint32_t>(lane) * 128u;  // this lane's row of the patch
       tmem_ld_wait();
@@ -221,7 +223,7 @@ __device__ __forceinline__ void epilogue_rows(const KernelParams& p, uint32_t ta
         st_shared_v4(patch_w + (static_cast<uint32_t>((2 * q4) ^ (lane & 7)) << 4), o[0].u);
         st_shared_v4(patch_w + (static_cast<uint32_t>((2 * q4 + 1) ^ (lane & 7)) << 4), o[1].u);
       }
-      if (c0 + 64 < p.tile_cols) {
+      if (c0 + 64 < c_end) {
 #pragma unroll
         for (int q4 = 0; q4 < 4; ++q4) tmem_ld_x16(taddr + c0 + 64 + 16 * q4, d[q4]);
       }
@@ -232,16 +234,19 @@ __device__ __forceinline__ void epilogue_rows(const KernelParams& p, uint32_t ta
       for (int i = 0; i < 8; ++i) {
         const int r = rsub + 4 * i;
         const uint4 v = ld_shared_v4(patch_b + static_cast<uint32_t>(r) * 128u + (static_cast<uint32_t>(chunk ^ (r & 7)) << 4));
-        if (flat_r[i] < p.numel && col < p.out_cols)
+        if (flat_r[i] < p.numel && col < p.out_cols && c0 + chunk * 8 < c_end)
           *reinterpret_cast<uint4*>(p.out + static_cast<long long>(flat_r[i]) * p.out_ld + col) = v;
       }
     }
   }
 }
 
-template <int kMode>  // 1 = gate_up, 2 = down
-__global__ void __launch_bounds__(kThreads, 1)
+template <int kMode, int kEpiWarps, int kGatherWarps>  // kMode: 1 = gate_up, 2 = down
+__global__ void __launch_bounds__(role_threads(kEpiWarps, kGatherWarps), 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b, const KernelParams p) {
+  constexpr int kWarpGather0 = kWarpEpilogue0 + kEpiWarps;
+  constexpr int kRowsPerStep = 4 * kGatherWarps;       // token rows one gather instruction of all warps covers
+  constexpr int kGatherSteps = BM / kRowsPerStep;       // copies per thread and stage
   extern __shared__ uint8_t smem_raw[];
   // operand stages want 1024-byte alignment in the shared window (swizzle atoms, descriptor base offset 0)
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -259,12 +264,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b, const KernelPara
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kMaxStages; ++s) {
-      mbar_init(&bar_full[s], 1 + 128);
+      mbar_init(&bar_full[s], 1 + 32 * kGatherWarps);
       mbar_init(&bar_empty[s], 1);
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&bar_tmem_full[a], 1);
-      mbar_init(&bar_tmem_empty[a], 4);
+      mbar_init(&bar_tmem_empty[a], kEpiWarps);
     }
     fence_mbar_init();
     tma_prefetch_desc(&tmap_b);
@@ -380,11 +385,17 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b, const KernelPara
       }
     }
     __syncwarp();
-  } else if (warp >= kWarpEpilogue0 && warp < kWarpEpilogue0 + 4) {
+  } else if (warp >= kWarpEpilogue0 && warp < kWarpEpilogue0 + kEpiWarps) {
     // ------------------------------------------------------------------ epilogue
     const int q = warp & 3;  // TMEM lane quarter this warp may read
     const int row_in_tile = q * 32 + lane;
-    const uint32_t patch = smem_u32(ring) + num_stages * stage_bytes + static_cast<uint32_t>(q) * (kPatchesPerWarp * kPatchBytes);
+    // with eight warps two share a lane quarter and take half of the tile's columns each
+    const int col_part = (warp - kWarpEpilogue0) / 4;
+    const int cols_per_part = kEpiWarps == 8 ? (p.tile_cols / 2 + 63) / 64 * 64 : p.tile_cols;
+    const int c_begin = col_part * cols_per_part;
+    const int c_end = min(p.tile_cols, c_begin + cols_per_part);
+    const uint32_t patch = smem_u32(ring) + num_stages * stage_bytes +
+                           static_cast<uint32_t>(warp - kWarpEpilogue0) * (kPatchesPerWarp * kPatchBytes);
     // A tile's permutation entry, routed weight and expert come from global memory, the weight through the entry.
     // These warps handle the tiles one after the other, so with a short main loop (a rank's slice of I in the down
     // pass: two K blocks) two dependent loads at the head of every tile would set the pace of the whole kernel:
@@ -423,9 +434,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b, const KernelPara
       }
       tc_fence_after_sync();
 
-      if (__any_sync(0xffffffffu, valid)) {
+      if (__any_sync(0xffffffffu, valid) && c_begin < c_end) {
         const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * kAccCols;
-        epilogue_rows<kMode>(p, taddr, pos, flat, valid, w, e, n0, patch);
+        epilogue_rows<kMode>(p, taddr, pos, flat, valid, w, e, n0, patch, c_begin, c_end);
       }
       tc_fence_before_sync();
       __syncwarp();
@@ -433,33 +444,33 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b, const KernelPara
     }
   } else if (warp >= kWarpGather0) {
     // ------------------------------------------------------------------ token-row gather (gate_up pass)
-    const int gw = warp - kWarpGather0;  // 0..3
+    const int gw = warp - kWarpGather0;  // 0..kGatherWarps-1
     const int sub = lane >> 3;           // row inside a group of 4
     const int ch = lane & 7;             // 16-byte chunk inside the 128-byte row
-    const int row0 = gw * 4 + sub;       // rows handled: row0 + 16*i
+    const int row0 = gw * 4 + sub;       // rows handled: row0 + kRowsPerStep*i
     const uint32_t swz = static_cast<uint32_t>((ch ^ (row0 & 7)) << 4);
     uint32_t s = 0, ph = 0;
     bool ok = true;
     // the permutation entries of the next tile are fetched one tile ahead (same reason as in the producer)
-    int flat_next[8];
+    int flat_next[kGatherSteps];
 #pragma unroll
-    for (int i = 0; i < 8; ++i)
+    for (int i = 0; i < kGatherSteps; ++i)
       flat_next[i] = static_cast<int>(blockIdx.x) < total_tiles
-                         ? p.sorted_ids[static_cast<long long>(blockIdx.x / p.n_tiles) * BM + row0 + 16 * i]
+                         ? p.sorted_ids[static_cast<long long>(blockIdx.x / p.n_tiles) * BM + row0 + kRowsPerStep * i]
                          : p.numel;
     for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
       const int m_blk = tile / p.n_tiles;
-      const __nv_bfloat16* src[8];
+      const __nv_bfloat16* src[kGatherSteps];
       const bool more = tile + static_cast<int>(gridDim.x) < total_tiles;
       const long long next_base = more ? static_cast<long long>((tile + gridDim.x) / p.n_tiles) * BM + row0 : 0;
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
+      for (int i = 0; i < kGatherSteps; ++i) {
         const int flat = flat_next[i];
-        if (more) flat_next[i] = p.sorted_ids[next_base + 16 * i];
+        if (more) flat_next[i] = p.sorted_ids[next_base + kRowsPerStep * i];
         if (kMode == 1)
           src[i] = flat < p.numel ? p.x + static_cast<long long>(flat / p.top_k) * p.K + ch * 8 : nullptr;
         else  // down pass: row p of the permuted intermediate
-          src[i] = flat < p.numel ? p.x + (static_cast<long long>(m_blk) * BM + row0 + 16 * i) * p.K + ch * 8 : nullptr;
+          src[i] = flat < p.numel ? p.x + (static_cast<long long>(m_blk) * BM + row0 + kRowsPerStep * i) * p.K + ch * 8 : nullptr;
       }
       for (int kb = 0; kb < num_kb; ++kb) {
         ok = mbar_wait(&bar_empty[s], ph ^ 1u);
@@ -471,8 +482,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b, const KernelPara
         const uint32_t a_base = smem_u32(ring + s * stage_bytes);
         const bool in_k = kb * BK + ch * 8 < p.K;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const uint32_t dst = a_base + static_cast<uint32_t>(row0 + 16 * i) * 128u + swz;
+        for (int i = 0; i < kGatherSteps; ++i) {
+          const uint32_t dst = a_base + static_cast<uint32_t>(row0 + kRowsPerStep * i) * 128u + swz;
           const bool live = in_k && src[i] != nullptr;
           cp_async_16(dst, live ? static_cast<const void*>(src[i] + kb * BK) : static_cast<const void*>(p.x),
                       live ? 16u : 0u);
@@ -495,14 +506,14 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b, const KernelPara
 }
 
 // ---------------------------------------------------------------- host side
-template <int kMode>
+template <int kMode, int kEpiWarps, int kGatherWarps>
 int ensure_smem_attr() {
   // the attribute belongs to the function on one device: a process that drives several GPUs sets it on each
   static bool done[64] = {false};
   int dev = 0;
   if (int st = check_cuda(cudaGetDevice(&dev), "cudaGetDevice")) return st;
   if (dev < 0 || dev >= 64 || !done[dev]) {
-    const cudaError_t e = cudaFuncSetAttribute(grouped_gemm_kernel<kMode>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit);
+    const cudaError_t e = cudaFuncSetAttribute(grouped_gemm_kernel<kMode, kEpiWarps, kGatherWarps>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit);
     if (e != cudaSuccess) return check_cuda(e, "cudaFuncSetAttribute(grouped_gemm_kernel)");
     if (dev >= 0 && dev < 64) done[dev] = true;
   }
@@ -626,7 +637,7 @@ int launch_grouped_gemm1(const GroupedGemmArgs& a, const __nv_bfloat16* x, const
   if (a.numel == 0 || a.max_m_blocks == 0) return kStatusOk;
   const int tile_cols = pick_gate_up_tile(a.inter, expected_m_blocks(a.numel, a.top_k, a.num_experts));
   const int mma_n = 2 * tile_cols;
-  if (int st = ensure_smem_attr<1>()) return st;
+  if (int st = ensure_smem_attr<1, 4, 4>()) return st;
 
   CUtensorMap map_b;
   const uint64_t dims[3] = {static_cast<uint64_t>(a.hidden), static_cast<uint64_t>(2 * a.inter), static_cast<uint64_t>(a.num_experts)};
@@ -646,7 +657,7 @@ int launch_grouped_gemm1(const GroupedGemmArgs& a, const __nv_bfloat16* x, const
   long long tiles = static_cast<long long>(a.max_m_blocks) * p.n_tiles;
   const int grid = static_cast<int>(tiles < device_sm_count() ? tiles : device_sm_count());
   const int smem_bytes = kBarrierBytes + 1024 + p.stages * p.stage_bytes;
-  if (int st = check_cuda(launch_pdl(grouped_gemm_kernel<1>, dim3(grid), dim3(kThreads), smem_bytes, stream, map_b, p),
+  if (int st = check_cuda(launch_pdl(grouped_gemm_kernel<1, 4, 4>, dim3(grid), dim3(role_threads(4, 4)), smem_bytes, stream, map_b, p),
                           "grouped_gemm gate_up launch"))
     return st;
   count_launches(1);
@@ -660,7 +671,12 @@ int launch_grouped_gemm2(const GroupedGemmArgs& a, const __nv_bfloat16* h_sorted
   if (a.numel == 0 || a.max_m_blocks == 0) return kStatusOk;
   if (a.hidden % 16 != 0) return set_error(kStatusInvalidArgument, "grouped GEMM down: hidden must be a multiple of 16");
   const int tile_cols = pick_down_tile(a.hidden, a.inter, expected_m_blocks(a.numel, a.top_k, a.num_experts));
-  if (int st = ensure_smem_attr<2>()) return st;
+  // A rank's thin slice of I (tensor parallel): the main loop of a tile is two to four K blocks and the epilogue
+  // warps set the pace, so eight of them share the tile (two per TMEM lane quarter, half the columns each) and two
+  // gather warps are enough for the short token rows; three operand stages then hold more than a tile.
+  const bool thin = a.inter <= 256 && tile_cols == 256;
+  const int epi_warps = thin ? 8 : 4;
+  if (int st = thin ? ensure_smem_attr<2, 8, 2>() : ensure_smem_attr<2, 4, 4>()) return st;
 
   CUtensorMap map_b;
   (void)rows_cap;
@@ -675,14 +691,15 @@ int launch_grouped_gemm2(const GroupedGemmArgs& a, const __nv_bfloat16* h_sorted
   p.out_cols = a.hidden; p.inter = a.inter; p.interleaved = 0;
   p.out = c3; p.out_ld = a.hidden; p.topk_w = topk_w; p.bias = w2_bias;
   p.alpha = 0.f; p.limit = 0.f; p.status = a.status;
-  pick_ring(p.mma_n, 4 * kPatchesPerWarp * kPatchBytes, &p.stages, &p.stage_bytes);
+  const int patch_bytes = epi_warps * kPatchesPerWarp * kPatchBytes;
+  pick_ring(p.mma_n, patch_bytes, &p.stages, &p.stage_bytes);
 
   long long tiles = static_cast<long long>(a.max_m_blocks) * p.n_tiles;
   const int grid = static_cast<int>(tiles < device_sm_count() ? tiles : device_sm_count());
-  const int smem_bytes = kBarrierBytes + 1024 + p.stages * p.stage_bytes + 4 * kPatchesPerWarp * kPatchBytes;
-  if (int st = check_cuda(launch_pdl(grouped_gemm_kernel<2>, dim3(grid), dim3(kThreads), smem_bytes, stream, map_b, p),
-                          "grouped_gemm down launch"))
-    return st;
+  const int smem_bytes = kBarrierBytes + 1024 + p.stages * p.stage_bytes + patch_bytes;
+  const cudaError_t le = thin ? launch_pdl(grouped_gemm_kernel<2, 8, 2>, dim3(grid), dim3(role_threads(8, 2)), smem_bytes, stream, map_b, p)
+                              : launch_pdl(grouped_gemm_kernel<2, 4, 4>, dim3(grid), dim3(role_threads(4, 4)), smem_bytes, stream, map_b, p);
+  if (int st = check_cuda(le, "grouped_gemm down launch")) return st;
   count_launches(1);
   return check_launch("grouped_gemm down");
 }
