@@ -28,6 +28,12 @@
 //   * pass 2 scales by the routed weight and writes bf16 rows at their flat index t*k+j; an epilogue warp owns
 //     one row per lane (the TMEM layout), so it turns 64 columns of its 32 rows around in a 4 KB shared-memory
 //     patch and stores whole 128-byte lines (four rows per instruction) instead of 32 scattered 16-byte pieces.
+//   * roles by warp: 0 = TMA producer, 1 = MMA issuer, then the epilogue warps, then the gather warps. The kernel is
+//     instantiated with four epilogue + four gather warps, and for the down pass over a rank's thin slice of I
+//     (two to four K blocks per tile, where the epilogue sets the pace) with eight epilogue warps - two per TMEM lane
+//     quarter, half of the tile's columns each - and two gather warps;
+//   * whatever a role reads from global memory per tile (expert id, permutation entries, routed weight) is fetched
+//     one or two tiles ahead.
 // The tile list is static: tile = blockIdx.x + i*gridDim.x over (m_block, n_tile), n fastest.
 #include <cmath>
 #include <cstdio>
