@@ -267,7 +267,10 @@ int moe_b200_ar_register_fused_buffer(int64_t handle, const int64_t* ptrs, int64
 int moe_b200_ar_register_ll_buffer(int64_t handle, const int64_t* ptrs, int64_t bytes);
 /* out = sum over ranks of inp (bf16/fp16/fp32 by element_size+is_bf16), fp32 accumulation in rank
  * order, identical bits on every rank. If reg_buffer != 0 the input is first copied there
- * (ops.all_reduce, custom_all_reduce_kernels.cu:64-107). algo: 0 auto, 1 one-shot, 2 two-shot. */
+ * (ops.all_reduce, custom_all_reduce_kernels.cu:64-107). algo: 0 auto (size and world size decide, as in
+ * custom_all_reduce.cuh:589-597, unless VLLM_CUSTOM_ALLREDUCE_ALGO forced a choice when the communicator was
+ * created), 1 one-shot, 2 two-shot, 3 one-shot with flag barriers (keeps moe_b200_ar_moe_sum_all_reduce off its
+ * flag-in-data path). */
 int moe_b200_ar_all_reduce(int64_t handle, const void* inp, void* out, int64_t numel, int dtype /*0 bf16,1 f16,2 f32*/,
                            int64_t reg_buffer, int64_t reg_buffer_bytes, int algo, int32_t* status_word, void* stream);
 /* k-slot sum of this rank's down-projection output fused with the all-reduce: one launch computes
