@@ -38,9 +38,11 @@ def single_rank_group():
     import torch.distributed as dist
     created = False
     if not dist.is_initialized():
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        os.environ.setdefault("MASTER_PORT", "29581")
-        dist.init_process_group("gloo", rank=0, world_size=1)
+        import socket
+        with socket.socket() as sock:  # any free port: the group has one member, nobody else needs to know it
+            sock.bind(("127.0.0.1", 0))
+            port = sock.getsockname()[1]
+        dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=0, world_size=1)
         created = True
     yield
     if created:
