@@ -95,6 +95,24 @@ def _worker(rank, world, port, q):
         full8 = O.fused_experts_fp8(x8, q13, s13, q2, s2, tw, ti).float()
         assert O.rel_l2(part8, full8) < 3e-2
 
+        # the row-parallel linear (o_proj): weight sharded on its input dimension, bias on rank 0 only, partial
+        # products summed over the ranks (nanovllm/layers/linear.py:155-201)
+        from layered_prefill_b200.linear import RowParallelLinear
+        car._ar_comm = None
+        gl = torch.Generator().manual_seed(11)
+        w_full = torch.randn(24, 16 * world, generator=gl)
+        b_full = torch.randn(24, generator=gl)
+        x_full = torch.randn(5, 16 * world, generator=gl)
+        lin = RowParallelLinear(16 * world, 24, bias=True)
+        assert lin.weight.shape == (24, 16) and (lin.tp_rank, lin.tp_size) == (rank, world)
+        lin.bias.data.zero_()
+        lin.weight_loader(lin.weight, w_full)
+        lin.weight_loader(lin.bias, b_full)
+        assert torch.equal(lin.weight.data, w_full[:, 16 * rank:16 * (rank + 1)])
+        assert torch.equal(lin.bias.data, b_full if rank == 0 else torch.zeros(24))
+        y = lin(x_full[:, 16 * rank:16 * (rank + 1)].contiguous())
+        assert torch.allclose(y, x_full @ w_full.t() + b_full, atol=1e-4)
+
         # mapping of checkpoint names to (param, shard) as the loader uses it
         m = FusedMoE.make_expert_params_mapping("gate_proj", "down_proj", "up_proj", num_experts=E)
         assert len(m) == 3 * E and m[0] == ("experts.w13_", "experts.0.gate_proj.", 0, "w1")
